@@ -1,0 +1,242 @@
+// extern "C" entry points of libegs_b200.so: argument validation, path selection, launches.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "egs_internal.cuh"
+
+namespace egs {
+
+static std::atomic<long long> g_launches{0};
+static thread_local char g_cuda_error[256] = "";
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+int fail_cuda(cudaError_t err, const char* where) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", where, cudaGetErrorString(err));
+  return EGS_ERR_CUDA;
+}
+
+bool valid_dtype(int d) { return d == EGS_F32 || d == EGS_F16 || d == EGS_BF16; }
+bool valid_index(int d) { return d == EGS_I16 || d == EGS_I32 || d == EGS_I64; }
+int elem_size(int d) { return d == EGS_F32 ? 4 : 2; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+constexpr long long kInt32Max = 2147483647LL;
+
+bool device_is_sm100() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached_ok = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (dev != cached_dev) {
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cached_dev = dev;
+    cached_ok = (major == 10);
+  }
+  return cached_ok != 0;
+}
+
+// The tensor-core kernels move rows with 16-byte copies: every row pitch must be a multiple of 16 bytes
+// and every base pointer 16-byte aligned.
+bool rowgemm_tensor_ok(const egs_dims& d, int dtype, const void* a, const void* w, const void* out) {
+  const int es = elem_size(dtype);
+  return (d.C * es) % 16 == 0 && (d.N * es) % 16 == 0 && aligned16(a) && aligned16(w) && aligned16(out);
+}
+
+int check_dims(const egs_dims* d) {
+  if (!d) return EGS_ERR_INVALID_ARGUMENT;
+  if (d->B < 0 || d->T < 0 || d->E < 0 || d->K < 0 || d->C < 0 || d->N < 0) return EGS_ERR_INVALID_ARGUMENT;
+  if (d->B * d->T > kInt32Max || d->B * d->E * d->K > kInt32Max || d->C > (1 << 24) || d->N > (1 << 24) ||
+      d->E > 65535 || d->B * d->K > kInt32Max)
+    return EGS_ERR_TOO_LARGE;
+  return EGS_OK;
+}
+
+int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, void* Out, const egs_dims* dims,
+                int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path, int32_t* status,
+                void* stream) {
+  if (int rc = check_dims(dims)) return rc;
+  if (!valid_dtype(dtype) || !valid_index(index_dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
+      (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32) ||
+      (path != EGS_PATH_AUTO && path != EGS_PATH_GENERIC && path != EGS_PATH_TENSOR))
+    return EGS_ERR_INVALID_ARGUMENT;
+  const egs_dims& d = *dims;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long out_rows = scatter ? d.B * d.T : d.B * d.E * d.K;
+  const size_t out_bytes = static_cast<size_t>(out_rows) * d.N * elem_size(dtype);
+  if (out_bytes == 0) return EGS_OK;
+  if (!Out) return EGS_ERR_INVALID_ARGUMENT;
+  const bool no_work = (d.B * d.E * d.K == 0);
+  if (!no_work && (!A || !W || !Ind) && d.C > 0) return EGS_ERR_INVALID_ARGUMENT;
+
+  if (scatter && zero_output) {
+    cudaError_t err = launch_fill_zero(Out, out_bytes, st);
+    if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+  }
+  if (no_work) return EGS_OK;
+  if (d.C == 0) {   // empty contraction: gather output is all zeros, scatter adds nothing
+    if (!scatter) {
+      cudaError_t err = launch_fill_zero(Out, out_bytes, st);
+      if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+    }
+    return EGS_OK;
+  }
+
+  RowGemmParams p{};
+  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.status = status;
+  p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
+  p.C = static_cast<int>(d.C); p.N = static_cast<int>(d.N);
+  p.M = static_cast<int>(d.B * d.K);
+  p.w_layout = w_layout; p.index_dtype = index_dtype;
+
+  const bool eligible = device_is_sm100() && rowgemm_tensor_ok(d, dtype, A, W, Out);
+  if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
+  const bool tensor = (path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible);
+  cudaError_t err;
+  if (tensor) {
+    const size_t smem = configure_tensor_rowgemm(p, dtype, precision);
+    err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
+  } else {
+    err = launch_generic_rowgemm(p, scatter, dtype, st);
+  }
+  if (err != cudaSuccess) return fail_cuda(err, scatter ? "gemm_scatter launch" : "gather_gemm launch");
+  return EGS_OK;
+}
+
+}  // namespace
+}  // namespace egs
+
+using namespace egs;
+
+extern "C" {
+
+int egs_version(void) { return 100; }
+
+const char* egs_status_string(int code) {
+  switch (code) {
+    case EGS_OK: return "ok";
+    case EGS_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case EGS_ERR_UNSUPPORTED: return "shape or device not eligible for the requested kernel family";
+    case EGS_ERR_CUDA: return "CUDA error";
+    case EGS_ERR_WORKSPACE: return "workspace missing or too small";
+    case EGS_ERR_TOO_LARGE: return "a size exceeds an internal limit";
+    default: return "unknown status";
+  }
+}
+
+const char* egs_last_cuda_error(void) { return g_cuda_error; }
+
+int64_t egs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int egs_gather_gemm(const void* X, const void* W, const void* Ind, void* Y, const egs_dims* dims, int w_layout,
+                    int dtype, int index_dtype, int precision, int path, int32_t* status_word, void* cuda_stream) {
+  return run_rowgemm(false, X, W, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, status_word,
+                     cuda_stream);
+}
+
+int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, const egs_dims* dims, int w_layout,
+                     int zero_output, int dtype, int index_dtype, int precision, int path, int32_t* status_word,
+                     void* cuda_stream) {
+  return run_rowgemm(true, Y, W, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path,
+                     status_word, cuda_stream);
+}
+
+size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype) {
+  if (dtype == EGS_F32 || E <= 0 || FG <= 0 || FD <= 0) return 0;
+  return static_cast<size_t>(E) * FG * FD * sizeof(float);
+}
+
+int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
+                int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision, int path,
+                void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  egs_dims d{B, T, E, K, FG, FD};
+  if (int rc = check_dims(&d)) return rc;
+  if (!valid_dtype(dtype) || !valid_index(index_dtype) ||
+      (out_layout != EGS_DW_GATHERED_ROWS && out_layout != EGS_DW_DIRECT_ROWS) ||
+      (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32) ||
+      (path != EGS_PATH_AUTO && path != EGS_PATH_GENERIC && path != EGS_PATH_TENSOR))
+    return EGS_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const size_t n_out = static_cast<size_t>(E) * FG * FD;
+  if (n_out == 0) return EGS_OK;
+  if (!out) return EGS_ERR_INVALID_ARGUMENT;
+  const int es = elem_size(dtype);
+  if (B * K == 0) {   // nothing to sum: the gradient is zero
+    cudaError_t err = launch_fill_zero(out, n_out * es, st);
+    return err == cudaSuccess ? EGS_OK : fail_cuda(err, "fill_zero");
+  }
+  if (!Xsrc || !Ysrc || !Ind) return EGS_ERR_INVALID_ARGUMENT;
+
+  DWeightParams p{};
+  p.Xsrc = Xsrc; p.Ysrc = Ysrc; p.Ind = Ind; p.out = out; p.status = status_word;
+  p.B = static_cast<int>(B); p.T = static_cast<int>(T); p.E = static_cast<int>(E); p.K = static_cast<int>(K);
+  p.FG = static_cast<int>(FG); p.FD = static_cast<int>(FD);
+  p.M = static_cast<int>(B * K);
+  p.out_layout = out_layout; p.index_dtype = index_dtype;
+
+  const bool eligible = device_is_sm100() && (FG * es) % 16 == 0 && (FD * es) % 16 == 0 && aligned16(Xsrc) &&
+                        aligned16(Ysrc) && aligned16(out) && (workspace == nullptr || aligned16(workspace));
+  if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
+  const bool tensor = (path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible);
+
+  size_t smem = 0;
+  if (tensor) {
+    smem = configure_tensor_dweight(p, dtype, precision);
+  } else {
+    // generic kernel: 64x64 tiles, contraction split so that the grid covers the SMs about twice
+    const long long tiles = ((FG + 63) / 64) * ((FD + 63) / 64) * E;
+    long long want = (2 * 148 + tiles - 1) / tiles;
+    const long long max_splits = (p.M + 15) / 16;
+    if (want > max_splits) want = max_splits;
+    if (want < 1) want = 1;
+    long long rows = (p.M + want - 1) / want;
+    rows = (rows + 15) / 16 * 16;
+    p.rows_per_split = static_cast<int>(rows);
+    p.splits = static_cast<int>((p.M + rows - 1) / rows);
+  }
+  if (static_cast<long long>(p.E) * p.splits > 65535) {   // grid.z limit: fall back to fewer splits
+    p.splits = 1;
+    p.rows_per_split = (p.M + 127) / 128 * 128;
+  }
+
+  cudaError_t err;
+  if (p.splits > 1) {
+    if (dtype == EGS_F32) {
+      p.acc = static_cast<float*>(out);
+    } else {
+      if (!workspace || workspace_bytes < n_out * sizeof(float)) return EGS_ERR_WORKSPACE;
+      p.acc = static_cast<float*>(workspace);
+    }
+    err = launch_fill_zero(p.acc, n_out * sizeof(float), st);
+    if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+  }
+  err = tensor ? launch_tensor_dweight(p, dtype, precision, smem, st) : launch_generic_dweight(p, dtype, st);
+  if (err != cudaSuccess) return fail_cuda(err, "dweight launch");
+  if (p.splits > 1 && dtype != EGS_F32) {
+    err = launch_convert_from_f32(p.acc, out, n_out, dtype, st);
+    if (err != cudaSuccess) return fail_cuda(err, "convert launch");
+  }
+  return EGS_OK;
+}
+
+int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers, int n_pointers) {
+  if (!dims || !valid_dtype(dtype) || op < 0 || op > 2) return 0;
+  if (!device_is_sm100()) return 0;
+  const int es = elem_size(dtype);
+  if ((dims->C * es) % 16 != 0 || (dims->N * es) % 16 != 0) return 0;
+  for (int i = 0; i < n_pointers; ++i)
+    if (pointers && pointers[i] && !aligned16(pointers[i])) return 0;
+  return 1;
+}
+
+int egs_fill_zero(void* p, size_t n_bytes, void* cuda_stream) {
+  if (n_bytes == 0) return EGS_OK;
+  if (!p) return EGS_ERR_INVALID_ARGUMENT;
+  cudaError_t err = launch_fill_zero(p, n_bytes, static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "fill_zero");
+}
+
+}  // extern "C"

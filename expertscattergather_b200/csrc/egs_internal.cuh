@@ -1,0 +1,91 @@
+// Internal declarations shared by the kernel files and the C-ABI file of libegs_b200.so.
+//
+// Vocabulary used across the kernels:
+//   slot        one routed token slot (b, e, k); its linear id is (b*E + e)*K + k
+//   token row   row b*T + t of a [B,T,F] tensor (X, Out, dX, dOut), t = Ind[slot]
+//   slot row    row `slot` of a [B,E,K,F] tensor (Y, dY)
+//   expert row  m in [0, B*K): the m-th slot of one expert, b = m / K, k = m % K
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/egs_b200.h"
+
+namespace egs {
+
+// ------------------------------------------------------------------------------------------------
+// element conversion
+// ------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Reads Ind[pos] for any of the three index widths.
+__device__ __forceinline__ long long load_index(const void* ind, int index_dtype, long long pos) {
+  if (index_dtype == EGS_I64) return static_cast<const long long*>(ind)[pos];
+  if (index_dtype == EGS_I32) return static_cast<const int*>(ind)[pos];
+  return static_cast<const short*>(ind)[pos];
+}
+
+// ------------------------------------------------------------------------------------------------
+// parameter blocks (validated on the host: every product below fits in int32 unless typed int64)
+// ------------------------------------------------------------------------------------------------
+struct RowGemmParams {
+  const void* A;      // G: token rows [B*T, C]      S: slot rows [B*E*K, C]
+  const void* W;      // [E, C, N] (EGS_W_CN) or [E, N, C] (EGS_W_NC)
+  const void* Ind;    // [B, E, K]
+  void* Out;          // G: slot rows [B*E*K, N]     S: token rows [B*T, N]
+  int32_t* status;    // optional device status word
+  int B, T, E, K, C, N;
+  int M;              // expert rows per expert = B*K
+  int w_layout;
+  int index_dtype;
+  int BN;             // tensor path: tile width over N (multiple of 16, <= 256)
+  int stages;         // tensor path: pipeline depth
+};
+
+struct DWeightParams {
+  const void* Xsrc;   // token rows [B*T, FG]  (gathered through Ind)
+  const void* Ysrc;   // slot rows  [B*E*K, FD]
+  const void* Ind;
+  void* out;          // final output in the tensors' dtype
+  float* acc;         // fp32 accumulation buffer when splits > 1 (may alias out for fp32), else unused
+  int32_t* status;
+  int B, T, E, K, FG, FD;
+  int M;              // B*K
+  int out_layout;
+  int index_dtype;
+  int splits;         // number of row ranges the contraction is split into
+  int rows_per_split; // multiple of the stage depth
+  int BN;             // tensor path: tile width over FD
+  int stages;
+};
+
+// ------------------------------------------------------------------------------------------------
+// launchers implemented in the kernel files; each returns a cudaError_t from the launch
+// ------------------------------------------------------------------------------------------------
+cudaError_t launch_generic_rowgemm(const RowGemmParams& p, bool scatter, int dtype, cudaStream_t st);
+cudaError_t launch_generic_dweight(const DWeightParams& p, int dtype, cudaStream_t st);
+cudaError_t launch_fill_zero(void* ptr, size_t bytes, cudaStream_t st);
+cudaError_t launch_convert_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t st);
+
+// Tensor-core (tcgen05) family.  `configure_*` fills BN/stages and returns the dynamic shared memory size.
+size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision);
+size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision);
+cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision,
+                                  size_t smem_bytes, cudaStream_t st);
+cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precision, size_t smem_bytes,
+                                  cudaStream_t st);
+
+void count_launch(int n = 1);
+
+}  // namespace egs

@@ -1,0 +1,810 @@
+// tcgen05 / TMEM kernels for the three operators (sm_100a only).
+//
+// Common structure of both kernels (one CTA = one 128-row accumulator tile in tensor memory):
+//   warps 0..7  producers: index-driven 16-byte cp.async row gathers from global memory into shared
+//               memory, written directly in the 128-byte-swizzled layout the tensor core reads, through a
+//               ring of `stages` buffers; afterwards the same warps run the epilogue (tcgen05.ld of the
+//               accumulator, then vector stores or vector red.global.add into the destination rows)
+//   warp 8      allocates tensor memory; one lane issues tcgen05.mma per stage and commits to mbarriers
+// Stage hand-over uses mbarriers only (full[s]: producers -> MMA lane, empty[s]: MMA completion ->
+// producers, done: all MMAs -> epilogue).  Every wait is bounded: when it runs out the thread sets the
+// CTA's abort flag and EGS_STATUS_PIPELINE_TIMEOUT in the caller's status word, and all roles fall through
+// to the common exit, where tensor memory is released.
+//
+// Shared-memory tile format (one format for every operand): rows of 128-byte segments.  Element
+// (row r, 16-byte chunk c of the row) lives at
+//     base + (c / 8) * seg_stride + (r / 8) * 1024 + (r % 8) * 128 + ((c % 8) ^ (r % 8)) * 16
+// i.e. 8-row x 128-byte atoms with the hardware's 128B XOR swizzle, atoms of one segment column stacked
+// 1024 bytes apart, segment columns seg_stride = rows*128 bytes apart.  Read with a K-major descriptor
+// (rows = M or N index, SBO = 1024) the row is a contraction-contiguous operand; read with an MN-major
+// descriptor (rows = contraction index, LBO = seg_stride, SBO = 1024) the same bytes are a transposed
+// operand.  That is what lets gathered rows feed both  rows x W  (operators G, S) and  rows^T x rows
+// (operator D) without a transposing copy, and never materialises the gathered [B,E,K,I] block.
+//
+// float32 tensors: kind::tf32.  EGS_PREC_STRICT splits every operand chunk in shared memory into
+// hi = top 19 bits and lo = tf32(x - hi) and issues lo*hi + hi*lo + hi*hi into the same accumulator, which
+// restores ~fp32 product accuracy (the reference computes fp32 dots with allow_tf32=False,
+// egs/triton_kernels.py:389).  16-bit tensors: kind::f16 with fp32 accumulation.
+#include "egs_internal.cuh"
+
+namespace egs {
+
+namespace {
+
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kThreads = kProducerThreads + 32;
+constexpr int kTileM = 128;
+constexpr int kMaxStages = 4;
+constexpr uint32_t kHeaderBytes = 2048;
+constexpr size_t kSmemBudget = 200 * 1024;
+constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 clocks
+
+struct __align__(16) SmemHeader {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  int row_a[kTileM];   // rowgemm: source row index per tile row (-1 = masked)
+  int row_o[kTileM];   // rowgemm: destination row index per tile row (-1 = masked)
+};
+static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header does not fit");
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+  }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this or another thread ran out of time).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          int32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (((++spins) & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1u;
+        if (status) atomicOr(status, EGS_STATUS_PIPELINE_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 16 consecutive fp32 accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;   // descriptor version of this architecture
+  d |= static_cast<uint64_t>(2) << 61;   // layout type: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: fp32 accumulator, A and B of one format (0 f16, 1 bf16, 2 tf32).
+__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t a_mn_major, uint32_t b_mn_major, uint32_t m,
+                                               uint32_t n) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+         ((m >> 4) << 24);
+}
+
+// Address of (row r, 16-byte chunk c) inside a tile in the format described at the top of the file.
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, uint32_t seg_stride, int r, int c) {
+  return base + static_cast<uint32_t>(c >> 3) * seg_stride + static_cast<uint32_t>(r >> 3) * 1024u +
+         static_cast<uint32_t>(r & 7) * 128u + (static_cast<uint32_t>((c & 7) ^ (r & 7)) << 4);
+}
+
+// In-place hi/lo split of one 16-byte chunk of float32 values (strict mode).
+__device__ __forceinline__ void split_chunk(uint32_t addr, uint32_t lo_offset) {
+  uint32_t v[4], lo[4];
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t hi = v[i] & 0xFFFFE000u;
+    const float rem = __uint_as_float(v[i]) - __uint_as_float(hi);
+    asm volatile("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo[i]) : "f"(rem));
+    v[i] = hi;
+  }
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr + lo_offset), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3])
+               : "memory");
+}
+
+template <typename T> struct Elem;
+template <> struct Elem<float> { static constexpr uint32_t fmt = 2; static constexpr bool tf32 = true; };
+template <> struct Elem<__half> { static constexpr uint32_t fmt = 0; static constexpr bool tf32 = false; };
+template <> struct Elem<__nv_bfloat16> { static constexpr uint32_t fmt = 1; static constexpr bool tf32 = false; };
+
+// ---- epilogue helpers: 16 fp32 accumulator values -> destination row --------------------------------
+__device__ __forceinline__ void store_vec(float* dst, const uint32_t (&r)[16], int nvalid) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    if (v * 4 < nvalid)
+      *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+}
+__device__ __forceinline__ uint32_t pack2(__half*, uint32_t a, uint32_t b) {
+  const __half2 h = __floats2half2_rn(__uint_as_float(a), __uint_as_float(b));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, uint32_t a, uint32_t b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* dst, const uint32_t (&r)[16], int nvalid) {
+#pragma unroll
+  for (int v = 0; v < 2; ++v)
+    if (v * 8 < nvalid)
+      *reinterpret_cast<uint4*>(dst + v * 8) =
+          make_uint4(pack2(dst, r[v * 8], r[v * 8 + 1]), pack2(dst, r[v * 8 + 2], r[v * 8 + 3]),
+                     pack2(dst, r[v * 8 + 4], r[v * 8 + 5]), pack2(dst, r[v * 8 + 6], r[v * 8 + 7]));
+}
+__device__ __forceinline__ void red_vec(float* dst, const uint32_t (&r)[16], int nvalid) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    if (v * 4 < nvalid)
+      asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 4), "f"(__uint_as_float(r[v * 4])),
+                   "f"(__uint_as_float(r[v * 4 + 1])), "f"(__uint_as_float(r[v * 4 + 2])),
+                   "f"(__uint_as_float(r[v * 4 + 3]))
+                   : "memory");
+}
+__device__ __forceinline__ void red_vec(__nv_bfloat16* dst, const uint32_t (&r)[16], int nvalid) {
+#pragma unroll
+  for (int v = 0; v < 2; ++v)
+    if (v * 8 < nvalid)
+      asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 8),
+                   "r"(pack2(dst, r[v * 8], r[v * 8 + 1])), "r"(pack2(dst, r[v * 8 + 2], r[v * 8 + 3])),
+                   "r"(pack2(dst, r[v * 8 + 4], r[v * 8 + 5])), "r"(pack2(dst, r[v * 8 + 6], r[v * 8 + 7]))
+                   : "memory");
+}
+__device__ __forceinline__ void red_vec(__half* dst, const uint32_t (&r)[16], int nvalid) {
+#pragma unroll
+  for (int v = 0; v < 2; ++v)
+    if (v * 8 < nvalid)
+      asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 8),
+                   "r"(pack2(dst, r[v * 8], r[v * 8 + 1])), "r"(pack2(dst, r[v * 8 + 2], r[v * 8 + 3])),
+                   "r"(pack2(dst, r[v * 8 + 4], r[v * 8 + 5])), "r"(pack2(dst, r[v * 8 + 6], r[v * 8 + 7]))
+                   : "memory");
+}
+
+__device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
+  uint32_t c = 32;
+  while (c < static_cast<uint32_t>(bn)) c <<= 1;
+  return c;
+}
+
+__device__ __forceinline__ char* aligned_smem(unsigned char* raw) {
+  const uint32_t a = smem_u32(raw);
+  return reinterpret_cast<char*>(raw) + ((1024u - (a & 1023u)) & 1023u);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Operators G and S.   grid = (ceil(M/128), ceil(N/BN), E)
+//   A rows (K-major): G gathers token rows through Ind, S reads slot rows
+//   B = W[e]:  EGS_W_NC -> rows n, contraction contiguous (K-major);  EGS_W_CN -> rows c, n contiguous (MN-major)
+//   epilogue:  G stores slot rows;  S adds to token rows with vector red.global.add
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool STRICT, bool SCATTER>
+__global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmParams p) {
+  constexpr int ES = sizeof(T);
+  constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
+  constexpr int UK = 32 / ES;         // contraction elements per tcgen05.mma
+  extern __shared__ unsigned char smem_raw[];
+  char* smem = aligned_smem(smem_raw);
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
+  const uint32_t tiles0 = smem_u32(smem) + kHeaderBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = blockIdx.z;
+  const int m0 = blockIdx.x * kTileM;
+  const int n0 = blockIdx.y * p.BN;
+  const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);       // MMA N of this tile (multiple of 16)
+  const int stages = p.stages;
+  const bool w_nc = (p.w_layout == EGS_W_NC);
+
+  const uint32_t a_bytes = kTileM * 128u;
+  const int nseg_b = (p.BN * ES + 127) / 128;
+  const uint32_t b_bytes = w_nc ? static_cast<uint32_t>(p.BN) * 128u : static_cast<uint32_t>(nseg_b) * KE * 128u;
+  const uint32_t stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
+  const uint32_t a_lo_off = a_bytes;                                   // strict: A_hi | A_lo | B_hi | B_lo
+  const uint32_t b_off = STRICT ? 2u * a_bytes : a_bytes;
+  const uint32_t b_lo_off = b_bytes;
+  const int nk = (p.C + KE - 1) / KE;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  // ---- set-up ----
+  // A launch that follows a timed-out one on the same status word does no work (keeps a broken pipeline
+  // from costing one wait limit per wave of CTAs).
+  if (tid == 0)
+    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+  __syncthreads();
+  if (hdr->abort_flag) return;
+  if (tid < kTileM) {
+    const int m = m0 + tid;
+    int ra = -1, ro = -1;
+    if (m < p.M) {
+      const int b = m / p.K, k = m - b * p.K;
+      const int slot = (b * p.E + e) * p.K + k;
+      const long long t = load_index(p.Ind, p.index_dtype, slot);
+      if (t >= 0 && t < p.T) {
+        const int tok = b * p.T + static_cast<int>(t);
+        ra = SCATTER ? slot : tok;
+        ro = SCATTER ? tok : slot;
+      } else {
+        if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+        if (!SCATTER) ro = slot;
+      }
+    }
+    hdr->row_a[tid] = ra;
+    hdr->row_o[tid] = ro;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), kProducerWarps);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&hdr->done), 1);
+    fence_mbar_init();
+  }
+  const uint32_t tmem_cols = tmem_cols_for(p.BN);
+  if (warp == kProducerWarps) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+
+  if (warp < kProducerWarps) {
+    // =========================== producers ===========================
+    const char* A = static_cast<const char*>(p.A);
+    const char* W = static_cast<const char*>(p.W);
+    const long long row_bytes_a = static_cast<long long>(p.C) * ES;
+    const int dist = stages - 1;
+    bool alive = true;
+
+    // visits every 16-byte chunk this thread owns in stage `kt`:  f(dst_hi_addr, src, valid, is_b)
+    auto for_each_chunk = [&](int kt, uint32_t stage_base, auto&& f) {
+      const int k0 = kt * KE;
+      {   // A: 128 rows x 8 chunks
+        const int cc = tid & 7;
+        const long long koff = static_cast<long long>(k0) * ES + cc * 16;
+        const bool kvalid = koff < row_bytes_a;
+#pragma unroll
+        for (int i = 0; i < kTileM / 32; ++i) {
+          const int r = (tid >> 3) + 32 * i;
+          const int ra = hdr->row_a[r];
+          const bool v = kvalid && ra >= 0;
+          f(tile_addr(stage_base, 0u, r, cc), v ? A + static_cast<long long>(ra) * row_bytes_a + koff : A, v, false);
+        }
+      }
+      if (w_nc) {   // B rows = n (BN rows x 8 chunks), contraction contiguous
+        const int cc = tid & 7;
+        const long long koff = static_cast<long long>(k0) * ES + cc * 16;
+        const bool kvalid = koff < row_bytes_a;
+        for (int r = tid >> 3; r < p.BN; r += kProducerThreads / 8) {
+          const bool v = kvalid && (n0 + r) < p.N;
+          const char* src = W + (static_cast<long long>(e) * p.N + n0 + r) * row_bytes_a + koff;
+          f(tile_addr(stage_base + b_off, 0u, r, cc), v ? src : W, v, true);
+        }
+      } else {      // B rows = contraction index (KE rows x nseg_b*8 chunks), n contiguous
+        const int cpr = nseg_b * 8;
+        const long long row_bytes_w = static_cast<long long>(p.N) * ES;
+        const long long noff0 = static_cast<long long>(n0) * ES;
+        for (int idx = tid; idx < KE * cpr; idx += kProducerThreads) {
+          const int r = idx / cpr, c = idx - r * cpr;
+          const long long noff = noff0 + c * 16;
+          const bool v = (k0 + r) < p.C && noff < row_bytes_w;
+          const char* src = W + (static_cast<long long>(e) * p.C + k0 + r) * row_bytes_w + noff;
+          f(tile_addr(stage_base + b_off, KE * 128u, r, c), v ? src : W, v, true);
+        }
+      }
+    };
+
+    for (int kt = 0; kt < nk + dist; ++kt) {
+      if (kt < nk && alive) {
+        const int slot = kt % stages, use = kt / stages;
+        if (use > 0) alive = mbar_wait(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status);
+        if (alive) {
+          for_each_chunk(kt, tiles0 + slot * stage_bytes,
+                         [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
+        }
+      }
+      cp_async_commit();
+      const int kc = kt - dist;
+      if (kc >= 0) {
+        cp_async_wait_pending(dist);
+        if (alive) {
+          if (STRICT) {
+            const int slot = kc % stages;
+            for_each_chunk(kc, tiles0 + slot * stage_bytes, [&](uint32_t dst, const char*, bool, bool is_b) {
+              split_chunk(dst, is_b ? b_lo_off : a_lo_off);
+            });
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
+        }
+      }
+    }
+    cp_async_wait_pending(0);
+
+    // =========================== epilogue ===========================
+    if (alive) alive = mbar_wait(smem_u32(&hdr->done), 0u, abort_flag, p.status);
+    // all lanes of a warp must take the tcgen05.ld together: make the decision warp-uniform
+    alive = __all_sync(0xffffffffu, alive);
+    if (alive) {
+      tc_fence_after();
+      const int lg = warp & 3, half = warp >> 2;
+      const int r = lg * 32 + lane;
+      const int ro = hdr->row_o[r];
+      const bool zero_row = (!SCATTER) && hdr->row_a[r] < 0;   // gather: masked source row -> zeros
+      T* out = static_cast<T*>(p.Out);
+      const int nch = bn >> 4;
+      for (int c = half; c < nch; c += 2) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
+        tmem_ld_wait();
+        const int col = n0 + c * 16;
+        const int nvalid = min(16, p.N - col);
+        if (ro >= 0 && nvalid > 0) {
+          if (zero_row) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0u;
+          }
+          T* dst = out + static_cast<long long>(ro) * p.N + col;
+          if (SCATTER) red_vec(dst, v, nvalid);
+          else store_vec(dst, v, nvalid);
+        }
+      }
+    }
+  } else {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(Elem<T>::fmt, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(bn));
+      bool ok = true;
+      for (int ks = 0; ks < nk && ok; ++ks) {
+        const int slot = ks % stages;
+        ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / stages) & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_hi = tiles0 + slot * stage_bytes;
+        const uint32_t b_hi = a_hi + b_off;
+        const int krem = p.C - ks * KE;
+        const int nkq = min(KE / UK, (krem + UK - 1) / UK);
+        for (int kq = 0; kq < nkq; ++kq) {
+          const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
+          const uint32_t a_k = kq * 32u;
+          const uint32_t b_k = w_nc ? kq * 32u : kq * (UK * 128u);
+          const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
+          const uint64_t ad = make_smem_desc(a_hi + a_k, 16u, 1024u);
+          const uint64_t bd = make_smem_desc(b_hi + b_k, b_lbo, 1024u);
+          if (STRICT) {
+            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + a_k, 16u, 1024u);
+            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + b_k, b_lbo, 1024u);
+            umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
+            umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
+            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
+          } else {
+            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
+          }
+        }
+        umma_commit(smem_u32(&hdr->empty[slot]));
+      }
+      if (ok) umma_commit(smem_u32(&hdr->done));
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Operator D.   grid = (ceil(FG/128), ceil(FD/BN), E*splits)
+//   accumulator tile P[f, g]: TMEM lane = f (feature of the gathered rows), column = g
+//   A = gathered token rows of Xsrc, B = slot rows of Ysrc; both consumed MN-major (rows = contraction)
+//   splits == 1: the tile is stored in the output dtype; splits > 1: red.global.add.f32 into p.acc
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool STRICT>
+__global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightParams p) {
+  constexpr int ES = sizeof(T);
+  constexpr int KR = 128 / ES;          // contraction rows per stage (4 MMAs of UK rows)
+  constexpr int UK = 32 / ES;           // contraction rows per tcgen05.mma
+  constexpr int NSEG_A = ES;            // 128 features * ES bytes / 128
+  constexpr int CPR_A = NSEG_A * 8;     // 16-byte chunks per A row
+  extern __shared__ unsigned char smem_raw[];
+  char* smem = aligned_smem(smem_raw);
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
+  const uint32_t tiles0 = smem_u32(smem) + kHeaderBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = blockIdx.z / p.splits;
+  const int split = blockIdx.z - e * p.splits;
+  const int f0 = blockIdx.x * kTileM;
+  const int g0 = blockIdx.y * p.BN;
+  const int bn = min(p.BN, ((p.FD - g0) + 15) & ~15);
+  const int stages = p.stages;
+  const int m_begin = split * p.rows_per_split;
+  const int m_end = min(p.M, m_begin + p.rows_per_split);
+  const int nk = (max(0, m_end - m_begin) + KR - 1) / KR;
+
+  const int nseg_b = (p.BN * ES + 127) / 128;
+  const uint32_t seg_stride = KR * 128u;
+  const uint32_t a_bytes = NSEG_A * seg_stride;
+  const uint32_t b_bytes = static_cast<uint32_t>(nseg_b) * seg_stride;
+  const uint32_t stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
+  const uint32_t a_lo_off = a_bytes;
+  const uint32_t b_off = STRICT ? 2u * a_bytes : a_bytes;
+  const uint32_t b_lo_off = b_bytes;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  if (tid == 0)
+    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+  __syncthreads();
+  if (hdr->abort_flag) return;
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), kProducerWarps);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&hdr->done), 1);
+    fence_mbar_init();
+  }
+  const uint32_t tmem_cols = tmem_cols_for(p.BN);
+  if (warp == kProducerWarps) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+
+  if (warp < kProducerWarps) {
+    const char* Xs = static_cast<const char*>(p.Xsrc);
+    const char* Ys = static_cast<const char*>(p.Ysrc);
+    const long long row_bytes_g = static_cast<long long>(p.FG) * ES;
+    const long long row_bytes_d = static_cast<long long>(p.FD) * ES;
+    const int dist = stages - 1;
+    const int cpr_b = nseg_b * 8;
+    bool alive = true;
+
+    auto for_each_chunk = [&](int kt, uint32_t stage_base, bool want_src, auto&& f) {
+      const int mrow0 = m_begin + kt * KR;
+      // A: KR contraction rows x CPR_A chunks of the 128 gathered features
+      for (int idx = tid; idx < KR * CPR_A; idx += kProducerThreads) {
+        const int r = idx / CPR_A, c = idx % CPR_A;
+        const int m = mrow0 + r;
+        const long long foff = static_cast<long long>(f0) * ES + c * 16;
+        bool v = false;
+        const char* src = Xs;
+        if (want_src && m < m_end && foff < row_bytes_g) {
+          const int b = m / p.K, k = m - b * p.K;
+          const long long t = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + e) * p.K + k);
+          if (t >= 0 && t < p.T) {
+            v = true;
+            src = Xs + (static_cast<long long>(b) * p.T + t) * row_bytes_g + foff;
+          } else if (p.status) {
+            atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+          }
+        }
+        f(tile_addr(stage_base, seg_stride, r, c), src, v, false);
+      }
+      // B: KR contraction rows x cpr_b chunks of the BN direct features
+      for (int idx = tid; idx < KR * cpr_b; idx += kProducerThreads) {
+        const int r = idx / cpr_b, c = idx - r * cpr_b;
+        const int m = mrow0 + r;
+        const long long goff = static_cast<long long>(g0) * ES + c * 16;
+        bool v = false;
+        const char* src = Ys;
+        if (want_src && m < m_end && goff < row_bytes_d) {
+          const int b = m / p.K, k = m - b * p.K;
+          v = true;
+          src = Ys + (static_cast<long long>(b * p.E + e) * p.K + k) * row_bytes_d + goff;
+        }
+        f(tile_addr(stage_base + b_off, seg_stride, r, c), src, v, true);
+      }
+    };
+
+    for (int kt = 0; kt < nk + dist; ++kt) {
+      if (kt < nk && alive) {
+        const int slot = kt % stages, use = kt / stages;
+        if (use > 0) alive = mbar_wait(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status);
+        if (alive) {
+          for_each_chunk(kt, tiles0 + slot * stage_bytes, true,
+                         [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
+        }
+      }
+      cp_async_commit();
+      const int kc = kt - dist;
+      if (kc >= 0) {
+        cp_async_wait_pending(dist);
+        if (alive) {
+          if (STRICT) {
+            const int slot = kc % stages;
+            for_each_chunk(kc, tiles0 + slot * stage_bytes, false, [&](uint32_t dst, const char*, bool, bool is_b) {
+              split_chunk(dst, is_b ? b_lo_off : a_lo_off);
+            });
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
+        }
+      }
+    }
+    cp_async_wait_pending(0);
+
+    // epilogue
+    if (alive && nk > 0) alive = mbar_wait(smem_u32(&hdr->done), 0u, abort_flag, p.status);
+    alive = __all_sync(0xffffffffu, alive);
+    if (alive) {
+      tc_fence_after();
+      const int lg = warp & 3, half = warp >> 2;
+      const int f = f0 + lg * 32 + lane;
+      const int nch = bn >> 4;
+      T* out = static_cast<T*>(p.out);
+      for (int c = half; c < nch; c += 2) {
+        uint32_t v[16];
+        if (nk > 0) {
+          tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        const int g = g0 + c * 16;
+        const int nvalid = min(16, p.FD - g);
+        if (f < p.FG && nvalid > 0) {
+          if (p.out_layout == EGS_DW_GATHERED_ROWS) {
+            const long long off = (static_cast<long long>(e) * p.FG + f) * p.FD + g;
+            if (p.splits > 1) red_vec(p.acc + off, v, nvalid);
+            else store_vec(out + off, v, nvalid);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (i < nvalid) {
+                const long long off = (static_cast<long long>(e) * p.FD + g + i) * p.FG + f;
+                if (p.splits > 1) atomicAdd(p.acc + off, __uint_as_float(v[i]));
+                else out[off] = from_f32<T>(__uint_as_float(v[i]));
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(Elem<T>::fmt, 1u, 1u, kTileM, static_cast<uint32_t>(bn));
+      bool ok = true;
+      for (int ks = 0; ks < nk && ok; ++ks) {
+        const int slot = ks % stages;
+        ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / stages) & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_hi = tiles0 + slot * stage_bytes;
+        const uint32_t b_hi = a_hi + b_off;
+        const int rrem = (m_end - m_begin) - ks * KR;
+        const int nkq = min(KR / UK, (rrem + UK - 1) / UK);
+        for (int kq = 0; kq < nkq; ++kq) {
+          const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
+          const uint32_t koff = kq * (UK * 128u);
+          const uint64_t ad = make_smem_desc(a_hi + koff, seg_stride, 1024u);
+          const uint64_t bd = make_smem_desc(b_hi + koff, seg_stride, 1024u);
+          if (STRICT) {
+            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + koff, seg_stride, 1024u);
+            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + koff, seg_stride, 1024u);
+            umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
+            umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
+            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
+          } else {
+            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
+          }
+        }
+        umma_commit(smem_u32(&hdr->empty[slot]));
+      }
+      if (ok && nk > 0) umma_commit(smem_u32(&hdr->done));
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+int pick_stages(size_t stage_bytes) {
+  size_t s = (kSmemBudget - kHeaderBytes - 1024) / stage_bytes;
+  if (s > static_cast<size_t>(kMaxStages)) s = kMaxStages;
+  return static_cast<int>(s);
+}
+
+}  // namespace
+
+size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision) {
+  const int es = (dtype == EGS_F32) ? 4 : 2;
+  const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
+  const int ke = 128 / es;
+  int bn = (p.N + 15) & ~15;
+  const int cap = strict ? 128 : 256;
+  if (bn > cap) bn = cap;
+  p.BN = bn;
+  const size_t a_bytes = kTileM * 128;
+  const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
+  const size_t b_bytes = (p.w_layout == EGS_W_NC) ? static_cast<size_t>(bn) * 128 : nseg_b * ke * 128;
+  const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
+  p.stages = pick_stages(stage_bytes);
+  return 1024 + kHeaderBytes + p.stages * stage_bytes;
+}
+
+size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
+  const int es = (dtype == EGS_F32) ? 4 : 2;
+  const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
+  const int kr = 128 / es;
+  int bn = (p.FD + 15) & ~15;
+  const int cap = strict ? 128 : 256;
+  if (bn > cap) bn = cap;
+  p.BN = bn;
+  const size_t seg_stride = static_cast<size_t>(kr) * 128;
+  const size_t a_bytes = es * seg_stride;
+  const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
+  const size_t stage_bytes = (a_bytes + nseg_b * seg_stride) * (strict ? 2 : 1);
+  p.stages = pick_stages(stage_bytes);
+  // split the contraction so that the grid fills the 148 SMs about twice over
+  const long long tiles = static_cast<long long>((p.FG + kTileM - 1) / kTileM) * ((p.FD + bn - 1) / bn) * p.E;
+  long long want = (2 * 148 + tiles - 1) / tiles;
+  const long long max_splits = (p.M + kr - 1) / kr;
+  if (want > max_splits) want = max_splits;
+  if (want < 1) want = 1;
+  long long rows = (p.M + want - 1) / want;
+  rows = (rows + kr - 1) / kr * kr;
+  if (rows < kr) rows = kr;
+  p.rows_per_split = static_cast<int>(rows);
+  p.splits = static_cast<int>((p.M + rows - 1) / rows);
+  if (p.splits < 1) p.splits = 1;
+  return 1024 + kHeaderBytes + p.stages * stage_bytes;
+}
+
+template <typename K>
+static cudaError_t set_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+}
+
+cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision, size_t smem_bytes,
+                                  cudaStream_t st) {
+  dim3 grid((p.M + kTileM - 1) / kTileM, (p.N + p.BN - 1) / p.BN, p.E);
+  dim3 block(kThreads);
+  cudaError_t err = cudaSuccess;
+#define EGS_LAUNCH(TY, STRICT)                                                                  \
+  do {                                                                                          \
+    if (scatter) {                                                                              \
+      err = set_smem(tensor_rowgemm_kernel<TY, STRICT, true>, smem_bytes);                      \
+      if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, true><<<grid, block, smem_bytes, st>>>(p);  \
+    } else {                                                                                    \
+      err = set_smem(tensor_rowgemm_kernel<TY, STRICT, false>, smem_bytes);                     \
+      if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, false><<<grid, block, smem_bytes, st>>>(p); \
+    }                                                                                           \
+  } while (0)
+  if (dtype == EGS_F32) {
+    if (precision == EGS_PREC_STRICT) EGS_LAUNCH(float, true);
+    else EGS_LAUNCH(float, false);
+  } else if (dtype == EGS_F16) {
+    EGS_LAUNCH(__half, false);
+  } else {
+    EGS_LAUNCH(__nv_bfloat16, false);
+  }
+#undef EGS_LAUNCH
+  if (err != cudaSuccess) return err;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precision, size_t smem_bytes, cudaStream_t st) {
+  dim3 grid((p.FG + kTileM - 1) / kTileM, (p.FD + p.BN - 1) / p.BN, p.E * p.splits);
+  dim3 block(kThreads);
+  cudaError_t err = cudaSuccess;
+#define EGS_LAUNCH(TY, STRICT)                                                          \
+  do {                                                                                  \
+    err = set_smem(tensor_dweight_kernel<TY, STRICT>, smem_bytes);                      \
+    if (err == cudaSuccess) tensor_dweight_kernel<TY, STRICT><<<grid, block, smem_bytes, st>>>(p); \
+  } while (0)
+  if (dtype == EGS_F32) {
+    if (precision == EGS_PREC_STRICT) EGS_LAUNCH(float, true);
+    else EGS_LAUNCH(float, false);
+  } else if (dtype == EGS_F16) {
+    EGS_LAUNCH(__half, false);
+  } else {
+    EGS_LAUNCH(__nv_bfloat16, false);
+  }
+#undef EGS_LAUNCH
+  if (err != cudaSuccess) return err;
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace egs

@@ -1,0 +1,168 @@
+"""Autograd functions and dispatcher ops of the expert gather / scatter path.
+
+Host-side mirror of the reference's L1 layer (``egs/triton_kernels.py:358-639``): the same four
+dispatcher ops in namespace ``mylib`` with the same schemas (``:362,395,444,478``), the same fake
+(shape-propagation) registrations for ``torch.compile`` (``:527-567``), the same module-level handles
+``expert_{gather,scatter}_{forward,backward}_call`` (``:26-29,569-578``), ``create_kernels()`` and the two
+``torch.autograd.Function`` classes (``:581-639``).  The bodies call the sm_100a kernels of
+``libegs_b200.so`` instead of Triton; there is no autotuning and no CPU path.
+
+Differences from the reference, on purpose:
+* the scatter forward output is zero-filled (the reference allocates it with ``torch.empty`` and only
+  adds to it, ``:457``);
+* non-contiguous inputs (for example the stride-0 gradient of ``.sum()``) are made contiguous first;
+* ``out_dtype`` is accepted and ignored exactly like the reference ignores it: tensors are read in their own
+  dtype, accumulated in float32 and written in the input dtype (``:375,457``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+__all__ = ["create_kernels", "ExpertGatherFunction", "ExpertScatterFunction", "dtype_to_type_id",
+           "expert_gather_forward_call", "expert_gather_backward_call", "expert_scatter_forward_call",
+           "expert_scatter_backward_call", "OP_NAMESPACE"]
+
+dtype_to_type_id = ops.dtype_to_type_id
+
+expert_gather_forward_call = None
+expert_gather_backward_call = None
+expert_scatter_forward_call = None
+expert_scatter_backward_call = None
+OP_NAMESPACE = None
+
+
+# ---- op bodies ---------------------------------------------------------------------------------------
+
+def _gather_forward(X, W, Ind, out_dtype):
+    # Y = gather(X) @ W_g                                      (reference: egs/triton_kernels.py:367-392)
+    return ops.gather_gemm(X, W, Ind, w_layout="cn")
+
+
+def _gather_backward(X, W, Ind, grad_output, out_dtype):
+    # dX = scatter(dY @ W_g^T), dW_g = gather(X)^T @ dY        (reference: egs/triton_kernels.py:400-441)
+    T = X.shape[1]
+    grad_output = grad_output.contiguous()
+    grad_X = ops.gemm_scatter(grad_output, W, Ind, T, w_layout="nc")
+    grad_W = ops.dweight(X, grad_output, Ind, out_layout="gathered_rows")
+    return grad_X, grad_W
+
+
+def _scatter_forward(Y, W, Ind, T, out_dtype):
+    # Out = scatter(Y @ W_s)                                   (reference: egs/triton_kernels.py:449-474)
+    return ops.gemm_scatter(Y, W, Ind, T, w_layout="cn")
+
+
+def _scatter_backward(Y, W, Ind, grad_X, out_dtype):
+    # dY = gather(dOut) @ W_s^T, dW_s = Y^T @ gather(dOut)     (reference: egs/triton_kernels.py:483-525)
+    grad_X = grad_X.contiguous()
+    grad_Y = ops.gather_gemm(grad_X, W, Ind, w_layout="nc")
+    grad_W = ops.dweight(grad_X, Y, Ind, out_layout="direct_rows")
+    return grad_Y, grad_W
+
+
+# ---- fake (meta) implementations: shapes and dtypes only --------------------------------------------
+
+def _gather_forward_fake(X, W, Ind, out_dtype):
+    return X.new_empty((X.shape[0], W.shape[0], Ind.shape[2], W.shape[2]))
+
+
+def _gather_backward_fake(X, W, Ind, grad_output, out_dtype):
+    return torch.empty_like(X), torch.empty_like(W)
+
+
+def _scatter_forward_fake(Y, W, Ind, T, out_dtype):
+    return Y.new_empty((Y.shape[0], T, W.shape[2]))
+
+
+def _scatter_backward_fake(Y, W, Ind, grad_X, out_dtype):
+    return torch.empty_like(Y), torch.empty_like(W)
+
+
+_SCHEMAS = {
+    "expert_gather_forward_call_fn": ("(Tensor X, Tensor W, Tensor Ind, ScalarType out_dtype) -> Tensor",
+                                      _gather_forward, _gather_forward_fake),
+    "expert_gather_backward_call_fn": ("(Tensor X, Tensor W, Tensor Ind, Tensor grad_output, ScalarType out_dtype)"
+                                       " -> (Tensor, Tensor)", _gather_backward, _gather_backward_fake),
+    "expert_scatter_forward_call_fn": ("(Tensor Y, Tensor W, Tensor Ind, int T, ScalarType out_dtype) -> Tensor",
+                                       _scatter_forward, _scatter_forward_fake),
+    "expert_scatter_backward_call_fn": ("(Tensor Y, Tensor W, Tensor Ind, Tensor grad_X, ScalarType out_dtype)"
+                                        " -> (Tensor, Tensor)", _scatter_backward, _scatter_backward_fake),
+}
+
+
+def _define_ops(namespace: str) -> None:
+    for name, (schema, impl, fake) in _SCHEMAS.items():
+        qual = f"{namespace}::{name}"
+        torch.library.define(qual, schema)
+        torch.library.impl(qual, "default")(impl)
+        torch.library.register_fake(qual)(fake)
+
+
+def create_kernels() -> None:
+    """Defines the four dispatcher ops once per process and binds the module-level call handles.
+
+    Same role and guard as the reference's ``create_kernels`` (``egs/triton_kernels.py:32-36``); here there is
+    nothing to JIT, so it only registers the ops.  If another library already owns ``mylib::expert_*`` in this
+    process (the reference itself), the ops are registered under ``egs_b200`` instead.
+    """
+    global expert_gather_forward_call, expert_gather_backward_call
+    global expert_scatter_forward_call, expert_scatter_backward_call, OP_NAMESPACE
+    if expert_gather_forward_call is not None:
+        return
+    namespace = "mylib"
+    try:
+        _define_ops(namespace)
+    except RuntimeError:
+        namespace = "egs_b200"
+        _define_ops(namespace)
+    lib = getattr(torch.ops, namespace)
+    OP_NAMESPACE = namespace
+    expert_gather_forward_call = lib.expert_gather_forward_call_fn
+    expert_gather_backward_call = lib.expert_gather_backward_call_fn
+    expert_scatter_forward_call = lib.expert_scatter_forward_call_fn
+    expert_scatter_backward_call = lib.expert_scatter_backward_call_fn
+
+
+class ExpertGatherFunction(torch.autograd.Function):
+    """``Y[b,e,k,j] = sum_i X[b, Ind[b,e,k], i] * W[e,i,j]`` with X [B,T,I], W [E,I,J], Ind [B,E,K].
+
+    Same call signature and return convention as the reference class (``egs/triton_kernels.py:581-608``):
+    ``apply(X, W, Ind, out_type=torch.float32)``; backward returns ``(grad_X, grad_W, None, None)`` and always
+    computes both gradients.
+    """
+
+    @staticmethod
+    def forward(ctx, X, W, Ind, out_type=torch.float32):
+        create_kernels()
+        ctx.save_for_backward(X, W, Ind)
+        ctx.dtype = out_type
+        return expert_gather_forward_call(X, W, Ind, out_type)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        X, W, Ind = ctx.saved_tensors
+        grad_X, grad_W = expert_gather_backward_call(X, W, Ind, grad_output, ctx.dtype)
+        return grad_X, grad_W, None, None
+
+
+class ExpertScatterFunction(torch.autograd.Function):
+    """``Out[b,t,i] = sum_{e,k: Ind[b,e,k]=t} sum_j Y[b,e,k,j] * W[e,j,i]`` with Y [B,E,K,J], W [E,J,I].
+
+    Same call signature as the reference class (``egs/triton_kernels.py:610-639``):
+    ``apply(Y, W, Ind, T, out_type=torch.float32)``; backward returns ``(grad_Y, grad_W, None, None, None)``.
+    """
+
+    @staticmethod
+    def forward(ctx, Y, W, Ind, T, out_type=torch.float32):
+        create_kernels()
+        ctx.save_for_backward(Y, W, Ind)
+        ctx.dtype = out_type
+        return expert_scatter_forward_call(Y, W, Ind, int(T), out_type)
+
+    @staticmethod
+    def backward(ctx, grad_X):
+        Y, W, Ind = ctx.saved_tensors
+        grad_Y, grad_W = expert_scatter_backward_call(Y, W, Ind, grad_X, ctx.dtype)
+        return grad_Y, grad_W, None, None, None

@@ -1,0 +1,246 @@
+"""Tensor-level host API over the C ABI: the three operators G, S, D on torch CUDA tensors.
+
+The functions allocate outputs with torch (so every buffer belongs to torch's caching allocator, as in the
+reference's launch wrappers, ``egs/triton_kernels.py:375,408-409,457,491-492``), pass raw pointers, sizes
+and the current CUDA stream to ``libegs_b200.so`` and return without synchronising.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+__all__ = ["gather_gemm", "gemm_scatter", "dweight", "set_precision", "get_precision", "set_path", "get_path",
+           "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
+
+_PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
+_PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR}
+_state = {
+    "precision": os.environ.get("EGS_B200_PRECISION", "strict").lower(),
+    "path": os.environ.get("EGS_B200_PATH", "auto").lower(),
+    "debug": os.environ.get("EGS_B200_DEBUG", "0") not in ("0", "", "false"),
+}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def set_precision(mode: str) -> None:
+    """'strict' (float32 products as accurate as fp32 FMA; the default, matching the reference's
+    ``allow_tf32=False``, ``egs/triton_kernels.py:389``) or 'tf32' (single TF32 product)."""
+    if mode not in _PRECISIONS:
+        raise ValueError(f"unknown precision {mode!r}")
+    _state["precision"] = mode
+
+
+def get_precision() -> str:
+    return _state["precision"]
+
+
+def set_path(path: str) -> None:
+    """'auto' (tensor-core kernels when the shape is eligible), 'generic' or 'tensor'."""
+    if path not in _PATHS:
+        raise ValueError(f"unknown path {path!r}")
+    _state["path"] = path
+
+
+def get_path() -> str:
+    return _state["path"]
+
+
+def dtype_to_type_id(dtype: torch.dtype) -> int:
+    """float32 -> 0, float16 -> 1, bfloat16 -> 2; anything else raises ValueError("Unknown dtype"),
+    as ``dtype_to_type_id`` in the reference does (``egs/triton_kernels.py:15-23``)."""
+    if dtype == torch.float32:
+        return _lib.F32
+    if dtype == torch.float16:
+        return _lib.F16
+    if dtype == torch.bfloat16:
+        return _lib.BF16
+    raise ValueError("Unknown dtype")
+
+
+def _index_tensor(Ind: torch.Tensor):
+    if Ind.dtype == torch.int64:
+        return Ind.contiguous(), _lib.I64
+    if Ind.dtype == torch.int32:
+        return Ind.contiguous(), _lib.I32
+    if Ind.dtype == torch.int16:
+        return Ind.contiguous(), _lib.I16
+    if Ind.dtype in (torch.int8, torch.uint8):
+        return Ind.to(torch.int32).contiguous(), _lib.I32
+    raise ValueError(f"Ind must be an integer tensor, got {Ind.dtype}")
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def reset_status(device=None) -> None:
+    for idx, w in _status_words.items():
+        if device is None or torch.device(device).index in (None, idx):
+            w.zero_()
+
+
+def check_status(device=None) -> None:
+    """Reads the device status word(s) (synchronises) and raises if a kernel flagged a problem."""
+    for idx, w in list(_status_words.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        v = int(w.item())
+        if v:
+            w.zero_()
+            msgs = []
+            if v & _lib.STATUS_INDEX_OUT_OF_RANGE:
+                msgs.append("an Ind value outside [0, T) was met (slot skipped)")
+            if v & _lib.STATUS_PIPELINE_TIMEOUT:
+                msgs.append("a bounded wait inside a tensor-core kernel ran out (results invalid)")
+            raise RuntimeError(f"egs kernels on cuda:{idx} reported: " + "; ".join(msgs))
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(_lib.load().egs_launch_count())
+
+
+def _require_cuda(*tensors) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("expert gather/scatter kernels need CUDA tensors (there is no CPU path)")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same CUDA device")
+    return dev
+
+
+def _stream_ptr(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _enums(precision, path):
+    prec = _PRECISIONS[precision if precision is not None else _state["precision"]]
+    pth = _PATHS[path if path is not None else _state["path"]]
+    return prec, pth
+
+
+def _w_dims(W: torch.Tensor, w_layout: str):
+    if w_layout == "cn":
+        return W.shape[0], W.shape[1], W.shape[2], _lib.W_CN
+    if w_layout == "nc":
+        return W.shape[0], W.shape[2], W.shape[1], _lib.W_NC
+    raise ValueError("w_layout must be 'cn' ([E,C,N]) or 'nc' ([E,N,C])")
+
+
+def gather_gemm(X, W, Ind, *, w_layout="cn", precision=None, path=None):
+    """Operator G: ``Y[b,e,k,:] = X[b, Ind[b,e,k], :] @ Wv[e]`` with ``Wv = W`` ('cn', W is [E,C,N]) or
+    ``W^T`` per expert ('nc', W is [E,N,C]).  X [B,T,C] -> Y [B,E,K,N], dtype of X."""
+    lib = _lib.load()
+    if X.dim() != 3 or W.dim() != 3 or Ind.dim() != 3:
+        raise ValueError("expected X[B,T,C], W[E,.,.], Ind[B,E,K]")
+    dev = _require_cuda(X, W, Ind)
+    if W.dtype != X.dtype:
+        raise ValueError("X and W must have the same dtype")
+    dt = dtype_to_type_id(X.dtype)
+    E, C, N, wl = _w_dims(W, w_layout)
+    B, T, Cx = X.shape
+    Bi, Ei, K = Ind.shape
+    if Cx != C or Ei != E or Bi != B:
+        raise ValueError(f"shape mismatch: X{tuple(X.shape)} W{tuple(W.shape)} Ind{tuple(Ind.shape)} ({w_layout})")
+    Xc, Wc = X.contiguous(), W.contiguous()
+    Ic, it = _index_tensor(Ind)
+    prec, pth = _enums(precision, path)
+    with torch.cuda.device(dev):
+        Y = torch.empty((B, E, K, N), device=dev, dtype=X.dtype)
+        dims = _lib.Dims(B, T, E, K, C, N)
+        rc = lib.egs_gather_gemm(Xc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), Y.data_ptr(), ctypes.byref(dims), wl, dt,
+                                 it, prec, pth, _status_word(dev).data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "egs_gather_gemm")
+    if _state["debug"]:
+        check_status(dev)
+    return Y
+
+
+def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=None):
+    """Operator S: ``Out[b, Ind[b,e,k], :] += Y[b,e,k,:] @ Wv[e]``; duplicates accumulate.
+    Y [B,E,K,C] -> Out [B,T,N].  ``out=None`` allocates and zero-fills; a given ``out`` is added to."""
+    lib = _lib.load()
+    if Y.dim() != 4 or W.dim() != 3 or Ind.dim() != 3:
+        raise ValueError("expected Y[B,E,K,C], W[E,.,.], Ind[B,E,K]")
+    dev = _require_cuda(Y, W, Ind)
+    if W.dtype != Y.dtype:
+        raise ValueError("Y and W must have the same dtype")
+    dt = dtype_to_type_id(Y.dtype)
+    E, C, N, wl = _w_dims(W, w_layout)
+    B, Ey, K, Cy = Y.shape
+    if Cy != C or Ey != E or tuple(Ind.shape) != (B, E, K):
+        raise ValueError(f"shape mismatch: Y{tuple(Y.shape)} W{tuple(W.shape)} Ind{tuple(Ind.shape)} ({w_layout})")
+    T = int(T)
+    Yc, Wc = Y.contiguous(), W.contiguous()
+    Ic, it = _index_tensor(Ind)
+    prec, pth = _enums(precision, path)
+    with torch.cuda.device(dev):
+        zero = 1
+        if out is None:
+            out = torch.empty((B, T, N), device=dev, dtype=Y.dtype)
+        else:
+            if tuple(out.shape) != (B, T, N) or out.dtype != Y.dtype or not out.is_contiguous():
+                raise ValueError("out must be a contiguous [B,T,N] tensor of Y's dtype")
+            zero = 0
+        dims = _lib.Dims(B, T, E, K, C, N)
+        rc = lib.egs_gemm_scatter(Yc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl,
+                                  zero, dt, it, prec, pth, _status_word(dev).data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "egs_gemm_scatter")
+    if _state["debug"]:
+        check_status(dev)
+    return out
+
+
+def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path=None):
+    """Operator D: ``P[e,f,g] = sum_{b,k} Xsrc[b, Ind[b,e,k], f] * Ysrc[b,e,k,g]``.
+    'gathered_rows' returns P [E,FG,FD]; 'direct_rows' returns P^T [E,FD,FG]."""
+    lib = _lib.load()
+    if Xsrc.dim() != 3 or Ysrc.dim() != 4 or Ind.dim() != 3:
+        raise ValueError("expected Xsrc[B,T,FG], Ysrc[B,E,K,FD], Ind[B,E,K]")
+    dev = _require_cuda(Xsrc, Ysrc, Ind)
+    if Xsrc.dtype != Ysrc.dtype:
+        raise ValueError("Xsrc and Ysrc must have the same dtype")
+    dt = dtype_to_type_id(Xsrc.dtype)
+    B, T, FG = Xsrc.shape
+    By, E, K, FD = Ysrc.shape
+    if By != B or tuple(Ind.shape) != (B, E, K):
+        raise ValueError(f"shape mismatch: Xsrc{tuple(Xsrc.shape)} Ysrc{tuple(Ysrc.shape)} Ind{tuple(Ind.shape)}")
+    if out_layout == "gathered_rows":
+        ol, shape = _lib.DW_GATHERED_ROWS, (E, FG, FD)
+    elif out_layout == "direct_rows":
+        ol, shape = _lib.DW_DIRECT_ROWS, (E, FD, FG)
+    else:
+        raise ValueError("out_layout must be 'gathered_rows' or 'direct_rows'")
+    Xc, Yc = Xsrc.contiguous(), Ysrc.contiguous()
+    Ic, it = _index_tensor(Ind)
+    prec, pth = _enums(precision, path)
+    with torch.cuda.device(dev):
+        out = torch.empty(shape, device=dev, dtype=Xsrc.dtype)
+        ws_bytes = int(lib.egs_dw_workspace_bytes(E, FG, FD, dt))
+        ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if ws_bytes else None
+        rc = lib.egs_dweight(Xc.data_ptr(), Yc.data_ptr(), Ic.data_ptr(), out.data_ptr(), B, T, E, K, FG, FD, ol, dt, it,
+                             prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
+                             _status_word(dev).data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "egs_dweight")
+    if _state["debug"]:
+        check_status(dev)
+    return out
+
+
+def tensor_path_eligible(op: str, B, T, E, K, C, N, dtype, tensors=()) -> bool:
+    """True if 'auto' would run the tcgen05 kernels for operator op ('G', 'S' or 'D') at these sizes."""
+    lib = _lib.load()
+    dims = _lib.Dims(B, T, E, K, C, N)
+    ptrs = (ctypes.c_void_p * max(1, len(tensors)))(*[t.data_ptr() for t in tensors])
+    return bool(lib.egs_tensor_path_eligible({"G": 0, "S": 1, "D": 2}[op], ctypes.byref(dims), dtype_to_type_id(dtype),
+                                             ptrs, len(tensors)))

@@ -1,0 +1,80 @@
+"""``ExpertGather`` and ``ExpertScatter``: parameter holders over the autograd functions.
+
+Drop-in for the reference's ``egs/torch_interface.py`` (constructor arguments, parameter names ``W`` and
+``bias``, shapes, initialisation and forward signatures are the same, so state dicts interchange).
+Deviations: the optional bias is tested with ``is not None`` (the reference's ``if self.bias:`` raises for any
+multi-element bias, ``egs/torch_interface.py:55,111``), the constructor does not query a CUDA device (the
+reference's Volta check at ``:23-33`` fails on a host without a GPU), and ``.to()`` is the standard
+``nn.Module.to`` (the reference re-wraps the parameters, ``:59-63``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from .kernels import ExpertGatherFunction, ExpertScatterFunction, create_kernels
+
+__all__ = ["ExpertGather", "ExpertScatter"]
+
+
+class ExpertGather(nn.Module):
+    """Gathers the K tokens routed to each expert and multiplies them by that expert's weights.
+
+    ``forward(x [B,T,I], Ind [B,E,K]) -> [B,E,K,J]``   (reference: ``egs/torch_interface.py:11-57``)
+    """
+
+    def __init__(self, E: int, I: int, J: int, bias: bool = False):
+        super().__init__()
+        self.E, self.I, self.J = E, I, J
+        self.W = nn.Parameter(torch.empty(E, I, J))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(E, 1, J))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+        create_kernels()
+
+    def reset_parameters(self) -> None:
+        bound = 1 / math.sqrt(self.I)
+        nn.init.uniform_(self.W, -bound, bound)
+        if self.bias is not None:
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, x: torch.Tensor, Ind: torch.Tensor) -> torch.Tensor:
+        y = ExpertGatherFunction.apply(x, self.W, Ind)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
+
+
+class ExpertScatter(nn.Module):
+    """Multiplies each expert's K rows by that expert's weights and adds them back at their token positions.
+
+    ``forward(Y [B,E,K,J], Ind [B,E,K], T) -> [B,T,I]``   (reference: ``egs/torch_interface.py:66-113``)
+    The initialisation bound uses ``1/sqrt(I)`` like the reference does (``:93``), although J is the fan-in.
+    """
+
+    def __init__(self, E: int, J: int, I: int, bias: bool = False):
+        super().__init__()
+        self.E, self.J, self.I = E, J, I
+        self.W = nn.Parameter(torch.empty(E, J, I))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(E, 1, I))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+        create_kernels()
+
+    def reset_parameters(self) -> None:
+        bound = 1 / math.sqrt(self.I)
+        nn.init.uniform_(self.W, -bound, bound)
+        if self.bias is not None:
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, Y: torch.Tensor, Ind: torch.Tensor, T: int) -> torch.Tensor:
+        out = ExpertScatterFunction.apply(Y, self.W, Ind, T)
+        if self.bias is not None:
+            out = out + self.bias   # broadcasts like the reference's expression: needs E == B or E == 1
+        return out

@@ -1,0 +1,129 @@
+/*
+ * egs_b200.h - C ABI of the B200 (sm_100a) fused expert gather / scatter library (libegs_b200.so).
+ *
+ * Every entry point takes raw device pointers, explicit sizes and a CUDA stream, launches on that
+ * stream and returns without synchronising.  Return value: 0 on success, otherwise one of the
+ * EGS_ERR_* codes below (text: egs_status_string).  No entry point allocates device memory, and the
+ * library keeps no device state besides what the caller passes in, unless its comment says so.
+ *
+ * Tensor layouts (all contiguous, row-major), as in the reference (README.md:7-9):
+ *     X / Out / dX : [B, T, I]        rows addressed by token id t in [0, T)
+ *     Y / dY       : [B, E, K, J]
+ *     Ind          : [B, E, K]        integer token ids, 16/32/64 bit
+ *     W            : [E, C, N] or [E, N, C] (see w_layout), C = contracted width, N = produced width
+ *
+ * The three operators and the six places the reference uses them (egs/triton_kernels.py):
+ *     G  gather-GEMM   : gather forward (:367-392)        and scatter backward dY  (:500-508)
+ *     S  GEMM-scatter  : scatter forward (:449-474)       and gather backward dX   (:416-424)
+ *     D  weight grad   : gather backward dW (:431-439)    and scatter backward dW  (:515-523)
+ */
+#ifndef EGS_B200_H_
+#define EGS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types; the numbering is the reference's dtype_to_type_id (egs/triton_kernels.py:15-23). */
+enum { EGS_F32 = 0, EGS_F16 = 1, EGS_BF16 = 2 };
+/* Index element types of Ind (the reference's tests pass int16, test_all.py:16; benchmarks int64). */
+enum { EGS_I16 = 0, EGS_I32 = 1, EGS_I64 = 2 };
+/* Arithmetic for float32 tensors.  STRICT reproduces IEEE-like float32 products (the reference runs
+ * its dots with allow_tf32=False, egs/triton_kernels.py:389): on the tensor-core path it is the
+ * three-product TF32 split.  TF32 is one TF32 product.  Ignored for 16-bit tensors (fp32 accumulate). */
+enum { EGS_PREC_STRICT = 0, EGS_PREC_TF32 = 1 };
+/* Kernel family.  AUTO picks the tcgen05 tensor-core kernels when the shape is eligible (row pitches
+ * multiples of 16 bytes, 16-byte aligned bases) and the generic CUDA-core kernels otherwise. */
+enum { EGS_PATH_AUTO = 0, EGS_PATH_GENERIC = 1, EGS_PATH_TENSOR = 2 };
+/* W memory layout relative to the contraction: CN = [E, C, N] (C rows of N), NC = [E, N, C]. */
+enum { EGS_W_CN = 0, EGS_W_NC = 1 };
+/* Output layout of the weight-gradient operator. */
+enum { EGS_DW_GATHERED_ROWS = 0 /* out[E, FG, FD] */, EGS_DW_DIRECT_ROWS = 1 /* out[E, FD, FG] */ };
+
+enum {
+  EGS_OK = 0,
+  EGS_ERR_INVALID_ARGUMENT = 1,   /* null pointer, negative size, unknown enum */
+  EGS_ERR_UNSUPPORTED = 2,        /* EGS_PATH_TENSOR requested for a shape that is not eligible */
+  EGS_ERR_CUDA = 3,               /* a CUDA runtime call or launch failed (see egs_last_cuda_error) */
+  EGS_ERR_WORKSPACE = 4,          /* workspace missing or smaller than egs_dw_workspace_bytes says */
+  EGS_ERR_TOO_LARGE = 5           /* a size exceeds an internal 32-bit or grid limit */
+};
+
+/* Bits a kernel may OR into the optional device status word (int32, caller-owned, may be NULL). */
+enum {
+  EGS_STATUS_INDEX_OUT_OF_RANGE = 1,  /* an Ind value outside [0,T) was met; that slot was skipped */
+  EGS_STATUS_PIPELINE_TIMEOUT = 2     /* a bounded wait inside a kernel ran out; results are invalid */
+};
+
+typedef struct egs_dims {
+  int64_t B, T, E, K;
+  int64_t C;  /* contracted feature width  (G: width of X rows;  S: width of Y rows) */
+  int64_t N;  /* produced feature width    (G: width of Y rows;  S: width of Out rows) */
+} egs_dims;
+
+/* Library version (major*10000 + minor*100 + patch).  Replaces nothing in the reference. */
+int egs_version(void);
+const char* egs_status_string(int code);
+/* Text of the last CUDA error this thread saw inside the library ("" if none). */
+const char* egs_last_cuda_error(void);
+
+/*
+ * Operator G:  Y[b,e,k,n] = sum_c X[b, Ind[b,e,k], c] * W(e,c,n)
+ * Replaces expert_gather_kernel + its launch wrappers:
+ *   gather forward       egs/triton_kernels.py:367-392  (X=X, W=W_g [E,I,J], w_layout=EGS_W_CN, C=I, N=J)
+ *   scatter backward dY  egs/triton_kernels.py:500-508  (X=dOut, W=W_s [E,J,I], w_layout=EGS_W_NC, C=I, N=J)
+ * Y is fully overwritten.  Out-of-range Ind values produce a zero row and set the status bit.
+ */
+int egs_gather_gemm(const void* X, const void* W, const void* Ind, void* Y, const egs_dims* dims,
+                    int w_layout, int dtype, int index_dtype, int precision, int path,
+                    int32_t* status_word, void* cuda_stream);
+
+/*
+ * Operator S:  Out[b,t,n] (+)= sum over (e,k) with Ind[b,e,k]==t of sum_c Y[b,e,k,c] * W(e,c,n)
+ * Replaces expert_scatter_kernel + its launch wrappers:
+ *   scatter forward      egs/triton_kernels.py:449-474  (W=W_s [E,J,I], w_layout=EGS_W_CN, C=J, N=I)
+ *   gather backward dX   egs/triton_kernels.py:416-424  (Y=dY, W=W_g [E,I,J], w_layout=EGS_W_NC, C=J, N=I)
+ * zero_output != 0: Out is zero-filled first on the same stream (the reference's forward forgets to,
+ * egs/triton_kernels.py:457); zero_output == 0: contributions are added to what Out holds.
+ * Duplicate token ids accumulate.  The additions are atomic and their order is not fixed.
+ */
+int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, const egs_dims* dims,
+                     int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path,
+                     int32_t* status_word, void* cuda_stream);
+
+/*
+ * Operator D:  P[e,f,g] = sum_{b,k} Xsrc[b, Ind[b,e,k], f] * Ysrc[b,e,k,g]      (f < FG, g < FD)
+ *   out_layout EGS_DW_GATHERED_ROWS : out[E, FG, FD] = P       (gather backward dW_g: Xsrc=X, Ysrc=dY)
+ *   out_layout EGS_DW_DIRECT_ROWS   : out[E, FD, FG] = P^T     (scatter backward dW_s: Xsrc=dOut, Ysrc=Y)
+ * Replaces expert_gather_scatter_dW_kernel + wrappers (egs/triton_kernels.py:431-439, :515-523).
+ * out is fully overwritten.  workspace: egs_dw_workspace_bytes() bytes of device scratch (may be
+ * NULL when that function returns 0); its contents on entry do not matter.
+ */
+int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out,
+                int64_t B, int64_t T, int64_t E, int64_t K, int64_t FG, int64_t FD,
+                int out_layout, int dtype, int index_dtype, int precision, int path,
+                void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
+
+/* Scratch bytes egs_dweight needs for these sizes (0 for float32 tensors).  No reference counterpart:
+ * the reference accumulates dW with atomics directly in the output dtype (egs/triton_kernels.py:356). */
+size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype);
+
+/* 1 if EGS_PATH_AUTO would take the tcgen05 tensor-core kernels for this operator and shape, else 0.
+ * op: 0 = G, 1 = S, 2 = D (for D pass C=FG, N=FD).  No reference counterpart (diagnostic). */
+int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers,
+                             int n_pointers);
+
+/* Zero-fills n bytes at p on the stream with the library's own fill kernel (what zero_output uses).
+ * Replaces the torch.zeros_like calls of the reference's wrappers (egs/triton_kernels.py:408-409). */
+int egs_fill_zero(void* p, size_t n_bytes, void* cuda_stream);
+
+/* Number of kernels the library has launched in this process since load (for launch accounting). */
+int64_t egs_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EGS_B200_H_ */
