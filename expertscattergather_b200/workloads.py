@@ -86,8 +86,11 @@ def indices_with_replacement(B, E, K, T, gen, dtype=torch.int16) -> torch.Tensor
     return torch.randint(0, T, (B, E, K), generator=gen).to(dtype)
 
 
-def make_inputs(w: Workload, B: int | None = None, integer_valued: bool = False):
+def make_inputs(w: Workload, B: int | None = None, integer_valued: bool = False, b0: int = 0):
     """Returns dict(X, Wg, Ws, Ind, G) on the CPU in ``w.dtype``.
+
+    ``b0`` is the global index of the first batch element to generate (a rank's slice of a sharded batch):
+    batch elements b0 .. b0+B-1 of the full workload are produced.
 
     ``B`` overrides the batch (a prefix-independent slice for CPU checks: each batch element is
     generated from its own sub-seed so a smaller B yields the same leading batch elements).
@@ -106,7 +109,7 @@ def make_inputs(w: Workload, B: int | None = None, integer_valued: bool = False)
     G = torch.empty(B, w.T, w.I)
     Ind = torch.empty(B, w.E, w.K, dtype=torch.int64)
     for b in range(B):
-        gb = torch.Generator().manual_seed(w.seed * 100003 + b)
+        gb = torch.Generator().manual_seed(w.seed * 100003 + b0 + b)
         if integer_valued:
             X[b] = torch.randint(-2, 3, (w.T, w.I), generator=gb).float()
             G[b] = torch.randint(-1, 2, (w.T, w.I), generator=gb).float()

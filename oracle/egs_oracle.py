@@ -136,14 +136,16 @@ def np_gather(X, W, Ind):
     B, T, I = X.shape
     _, E, K = Ind.shape
     rows = np.take_along_axis(X, Ind.reshape(B, E * K, 1), axis=1).reshape(B, E, K, I)
-    return np.einsum("beki,eij->bekj", rows, W)
+    # batched matmul over experts: [E, B*K, I] @ [E, I, J]
+    per_expert = np.matmul(rows.transpose(1, 0, 2, 3).reshape(E, B * K, I), W)
+    return np.ascontiguousarray(per_expert.reshape(E, B, K, -1).transpose(1, 0, 2, 3))
 
 
 def np_scatter(Y, W, Ind, T):
     """Operator S: (Y @ W[e]) added at rows Ind, duplicates accumulate (``egs/triton_kernels.py:618``)."""
     Y, W, Ind = _f64(Y), _f64(W), _idx(Ind)
     B, E, K, J = Y.shape
-    pre = np.einsum("bekj,eji->beki", Y, W)
+    pre = np.matmul(Y.transpose(1, 0, 2, 3).reshape(E, B * K, J), W).reshape(E, B, K, -1).transpose(1, 0, 2, 3)
     out = np.zeros((B, T, W.shape[-1]), dtype=np.float64)
     b_idx = np.broadcast_to(np.arange(B).reshape(B, 1, 1), Ind.shape)
     np.add.at(out, (b_idx.reshape(-1), Ind.reshape(-1)), pre.reshape(B * E * K, -1))
@@ -156,7 +158,8 @@ def np_dweight(Xsrc, Ysrc, Ind):
     B, T, I = Xsrc.shape
     _, E, K = Ind.shape
     rows = np.take_along_axis(Xsrc, Ind.reshape(B, E * K, 1), axis=1).reshape(B, E, K, I)
-    return np.einsum("beki,bekj->eij", rows, Ysrc)
+    a = rows.transpose(1, 3, 0, 2).reshape(E, I, B * K)
+    return np.matmul(a, Ysrc.transpose(1, 0, 2, 3).reshape(E, B * K, -1))
 
 
 def np_step(X, Wg, Ws, Ind, G):

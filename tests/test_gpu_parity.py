@@ -1,0 +1,280 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle and the committed reference
+outputs.  Bar: bit-exact for integer-valued inputs (index handling, collisions, zero fill); otherwise
+max|a-ref|/max|ref| <= 1e-5 (float32 strict), 2e-2 (tf32), 3e-2 (bf16/fp16)."""
+import numpy as np
+import pytest
+import torch
+
+import expertscattergather_b200 as egs
+from conftest import golden_names, load_golden
+from expertscattergather_b200 import ops, workloads
+from expertscattergather_b200.workloads import Workload
+from gpu_util import STEP_KEYS, compare_step, eligible, gpu_step, to_dev, tol_for
+from oracle import egs_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _paths_for(ins):
+    return ["generic", "tensor"] if eligible(ins) else ["generic"]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# committed outputs of the reference's torch modules
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", golden_names())
+def test_golden_full_step(cuda_device, name):
+    ins, refs, T, dtype = load_golden(name)
+    ref = {"Y": refs["f_Y"], "Out": refs["f_Out"], "dX": refs["f_dX"], "dWg": refs["f_dWg"], "dWs": refs["f_dWs"]}
+    for path in _paths_for(ins):
+        for precision in (("strict", "tf32") if dtype == torch.float32 and path == "tensor" else ("strict",)):
+            got = gpu_step(ins, cuda_device, path, precision)
+            if "integer" in name:
+                for k in ref:
+                    assert np.array_equal(got[k].float().numpy(), ref[k]), (name, path, precision, k)
+            else:
+                compare_step(got, ref, tol_for(dtype, precision), keys=tuple(ref), what=f"{name}/{path}/{precision}")
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_golden_modules_autograd(cuda_device, name):
+    """The reference's own test flow (test_all.py:13-77): module forward, loss, backward, compare three tensors."""
+    ins, refs, T, dtype = load_golden(name)
+    d = to_dev(ins, cuda_device)
+    E, I, J = ins["Wg"].shape
+    tol = tol_for(dtype, "strict")
+    gm = egs.ExpertGather(E, I, J).to(cuda_device)
+    gm.W = torch.nn.Parameter(d["Wg"].clone())
+    X = d["X"].clone().requires_grad_(True)
+    Y = gm(X, d["Ind"].to(torch.int16))
+    (Y * d["GY"]).sum().backward()
+    sm = egs.ExpertScatter(E, J, I).to(cuda_device)
+    sm.W = torch.nn.Parameter(d["Ws"].clone())
+    Yin = d["Yin"].clone().requires_grad_(True)
+    O = sm(Yin, d["Ind"].to(torch.int32), T)
+    (O * d["G"]).sum().backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = {"g_Y": Y, "g_dX": X.grad, "g_dW": gm.W.grad, "s_Out": O, "s_dY": Yin.grad, "s_dW": sm.W.grad}
+    for k, v in got.items():
+        v = v.detach().float().cpu().numpy()
+        if "integer" in name:
+            assert np.array_equal(v, refs[k]), (name, k)
+        else:
+            assert orc.rel_err(v, refs[k]) <= tol, (name, k, orc.rel_err(v, refs[k]))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the reference's random-shape tests (test_all.py:81-101): six dims drawn from [1,128), int16 ids with
+# replacement, loss = output.sum() (so the incoming gradient is a stride-0 expanded scalar)
+# ---------------------------------------------------------------------------------------------------------
+def _random_dims(seed):
+    g = torch.Generator().manual_seed(seed)
+    return [int(v) for v in torch.randint(1, 128, (6,), generator=g)]
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_shapes_gather_module(cuda_device, seed):
+    B, T, K, E, I, J = _random_dims(100 + seed)
+    g = torch.Generator().manual_seed(seed)
+    X = torch.randn(B, T, I, generator=g)
+    Ind = torch.randint(0, T, (B, E, K), generator=g).to(torch.int16)
+    m = egs.ExpertGather(E, I, J).to(cuda_device)
+    Xd = X.to(cuda_device).requires_grad_(True)
+    Y = m(Xd, Ind.to(cuda_device))
+    Y.sum().backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = orc.torch_gather_module_step(X, m.W.detach().cpu(), Ind, torch.ones(B, E, K, J))
+    for got, key in ((Y, "Y"), (Xd.grad, "dX"), (m.W.grad, "dW")):
+        got = got.detach().cpu()
+        assert orc.rel_err(got, ref[key]) <= 1e-5, (key, orc.rel_err(got, ref[key]))
+        assert torch.isclose(got, ref[key], atol=1e-3).all()      # the reference's own criterion (test_all.py:9-11)
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_shapes_scatter_module(cuda_device, seed):
+    B, T, K, E, I, J = _random_dims(200 + seed)
+    g = torch.Generator().manual_seed(seed)
+    Yin = torch.randn(B, E, K, J, generator=g)
+    Ind = torch.randint(0, T, (B, E, K), generator=g).to(torch.int16)
+    m = egs.ExpertScatter(E, J, I).to(cuda_device)
+    Yd = Yin.to(cuda_device).requires_grad_(True)
+    O = m(Yd, Ind.to(cuda_device), T)
+    O.sum().backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = orc.torch_scatter_module_step(Yin, m.W.detach().cpu(), Ind, T, torch.ones(B, T, I))
+    for got, key in ((O, "Out"), (Yd.grad, "dY"), (m.W.grad, "dW")):
+        got = got.detach().cpu()
+        assert orc.rel_err(got, ref[key]) <= 1e-5, (key, orc.rel_err(got, ref[key]))
+        assert torch.isclose(got, ref[key], atol=1e-3).all()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# bit-exact index handling on both kernel families
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("index", ["distinct", "replace", "zipf"])
+def test_integer_valued_inputs_are_bit_exact(cuda_device, dtype, index):
+    # ragged sizes: rows per expert (B*K = 222) not a multiple of the 128-row tile, 3 k-stages + tail
+    w = Workload("int", 6, 96, 5, 37, 104, 40, dtype, index, 4242)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    ref = orc.np_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    for path in ("generic", "tensor"):
+        for precision in (("strict", "tf32") if dtype == torch.float32 else ("strict",)):
+            if dtype != torch.float32:
+                # 16-bit outputs: |values| stay far below 256 only for Y; compare what is exactly representable
+                keys = ("Y", "dY")
+            else:
+                keys = STEP_KEYS
+            got = gpu_step(ins, cuda_device, path, precision)
+            for k in keys:
+                assert np.array_equal(got[k].double().numpy(), ref[k]), (path, precision, k)
+
+
+def test_identity_weights_return_the_gathered_rows(cuda_device):
+    B, T, E, K, I = 3, 50, 4, 20, 64
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(B, T, I, generator=g).bfloat16().float()        # bf16-representable: exact in one TF32 product
+    W = torch.eye(I).expand(E, I, I).contiguous()
+    Ind = torch.randint(0, T, (B, E, K), generator=g)
+    rows = torch.gather(X, 1, Ind.reshape(B, E * K, 1).expand(B, E * K, I)).reshape(B, E, K, I)
+    for path in ("generic", "tensor"):
+        for precision in ("strict", "tf32"):
+            Y = ops.gather_gemm(X.to(cuda_device), W.to(cuda_device), Ind.to(cuda_device), path=path, precision=precision)
+            assert torch.equal(Y.cpu(), rows), (path, precision)
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int16, torch.int32, torch.int64, torch.uint8])
+def test_index_dtypes(cuda_device, idx_dtype):
+    w = Workload("idx", 2, 100, 3, 9, 32, 16, torch.float32, "replace", 9)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    ref = orc.np_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    ins["Ind"] = ins["Ind"].to(idx_dtype)
+    for path in ("generic", "tensor"):
+        got = gpu_step(ins, cuda_device, path)
+        for k in STEP_KEYS:
+            assert np.array_equal(got[k].double().numpy(), ref[k]), (path, k)
+
+
+def test_scatter_output_is_zero_filled_every_call(cuda_device):
+    """The reference's forward adds into torch.empty (egs/triton_kernels.py:457); here repeated calls agree."""
+    w = Workload("z", 2, 300, 3, 5, 32, 16, torch.float32, "distinct", 3)
+    ins = to_dev(workloads.make_inputs(w, integer_valued=True), cuda_device)
+    Y = ops.gather_gemm(ins["X"], ins["Wg"], ins["Ind"])
+    junk = torch.full((64, 300, 32), 7.0, device=cuda_device)   # dirty the allocator's cache
+    del junk
+    a = ops.gemm_scatter(Y, ins["Ws"], ins["Ind"], 300).clone()
+    for _ in range(3):
+        junk = torch.full((2, 300, 32), 9.0, device=cuda_device)
+        del junk
+        b = ops.gemm_scatter(Y, ins["Ws"], ins["Ind"], 300)
+        assert torch.equal(a, b)
+    # untouched token rows are exactly zero
+    touched = torch.zeros(2, 300, dtype=torch.bool, device=cuda_device)
+    touched.scatter_(1, ins["Ind"].reshape(2, -1), True)
+    assert float(a[~touched].abs().sum()) == 0.0
+    # accumulate-into-given-output mode adds on top
+    c = ops.gemm_scatter(Y, ins["Ws"], ins["Ind"], 300, out=a.clone())
+    assert torch.equal(c, 2 * a)
+
+
+def test_out_of_range_index_is_skipped_and_reported(cuda_device):
+    w = Workload("oob", 2, 40, 3, 6, 32, 16, torch.float32, "distinct", 11)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    bad = ins["Ind"].clone()
+    bad[1, 2, 3] = 40          # == T
+    bad[0, 0, 0] = -1
+    good_mask = torch.ones_like(bad, dtype=torch.bool)
+    good_mask[1, 2, 3] = False
+    good_mask[0, 0, 0] = False
+    for path in ("generic", "tensor"):
+        ops.reset_status()
+        d = to_dev(ins, cuda_device)
+        Y = ops.gather_gemm(d["X"], d["Wg"], bad.to(cuda_device), path=path)
+        Yref = torch.from_numpy(orc.np_gather(ins["X"], ins["Wg"], ins["Ind"])).float()
+        Yref[~good_mask] = 0
+        assert torch.equal(Y.cpu(), Yref), path
+        Out = ops.gemm_scatter(Y, d["Ws"], bad.to(cuda_device), 40, path=path)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="outside"):
+            ops.check_status()
+        ops.check_status()      # the word is cleared by the failed check
+        safe = bad.clamp(0, 39)
+        ref = orc.np_scatter(Yref, ins["Ws"], safe, 40)
+        assert np.array_equal(Out.cpu().double().numpy(), ref), path
+
+
+# ---------------------------------------------------------------------------------------------------------
+# benchmark configurations (full size where the CPU checker finishes in seconds, batch slices otherwise)
+# ---------------------------------------------------------------------------------------------------------
+CONFIG_CASES = [("cfg0", None), ("cfg1-T256", None), ("cfg1-T1024", None), ("cfg1-T4096", 4), ("cfg1-T16384", 2),
+                ("cfg2", 2), ("cfg3", 1), ("cfg4", 2)]
+
+
+@pytest.mark.parametrize("name,B", CONFIG_CASES)
+def test_benchmark_configurations(cuda_device, name, B):
+    w = workloads.WORKLOADS[name]
+    ins = workloads.make_inputs(w, B=B)
+    ref = orc.torch_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    truth = orc.np_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"]) if w.dtype != torch.float32 else None
+    precisions = ("strict", "tf32") if w.dtype == torch.float32 else ("strict",)
+    for precision in precisions:
+        got = gpu_step(ins, cuda_device, "auto", precision)
+        tol = tol_for(w.dtype, precision)
+        compare_step(got, ref, tol, what=f"{name}/{precision} vs same-dtype torch path")
+        if truth is not None:
+            compare_step(got, truth, tol, what=f"{name}/{precision} vs float64 truth")
+    gen = gpu_step(ins, cuda_device, "generic", "strict")
+    compare_step(gen, ref, tol_for(w.dtype, "strict"), what=f"{name}/generic")
+
+
+def test_full_size_properties_cfg4_shard(cuda_device):
+    """Size-independent checks at the per-GPU size of the multi-GPU configuration (B=64 of cfg4), where the CPU
+    checker is too slow: (1) checksum of checksums - column sums of Out per batch element equal the column sums
+    of the per-slot products computed by a dense contraction; (2) linearity of the gather in X; (3) dW against a
+    dense contraction over a materialised gather, accumulated over batch chunks."""
+    w = workloads.WORKLOADS["cfg4"].with_batch(64)
+    ins = to_dev(workloads.make_inputs(w), cuda_device)
+    X, Wg, Ws, Ind, G = (ins[k] for k in ("X", "Wg", "Ws", "Ind", "G"))
+    Y = ops.gather_gemm(X, Wg, Ind)
+    Out = ops.gemm_scatter(Y, Ws, Ind, w.T)
+    dense = torch.einsum("bekj,eji->bi", Y.float(), Ws.float())
+    got = Out.float().sum(1)
+    assert float((got - dense).abs().max() / dense.abs().max()) <= 3e-2
+    X2 = torch.roll(X, 1, 0)
+    Ysum = ops.gather_gemm((X.float() + X2.float()).to(w.dtype), Wg, Ind)
+    Y2 = ops.gather_gemm(X2, Wg, Ind)
+    lin = (Ysum.float() - (Y.float() + Y2.float())).abs().max() / Ysum.float().abs().max()
+    assert float(lin) <= 3e-2
+    dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")
+    dWg = ops.dweight(X, dY, Ind)
+    dense_dw = torch.zeros(w.E, w.I, w.J, device=cuda_device)
+    for b0 in range(0, w.B, 8):
+        sl = slice(b0, b0 + 8)
+        rows = torch.gather(X[sl], 1, Ind[sl].reshape(8, -1, 1).expand(-1, -1, w.I)).reshape(8, w.E, w.K, w.I)
+        dense_dw += torch.einsum("beki,bekj->eij", rows.float(), dY[sl].float())
+    assert float((dWg.float() - dense_dw).abs().max() / dense_dw.abs().max()) <= 3e-2
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
+def test_no_gathered_intermediate_is_allocated(cuda_device):
+    """Peak device memory of a step stays below outputs + dW scratch + a small margin: no [B,E,K,I] block."""
+    w = workloads.WORKLOADS["cfg2"].with_batch(4)
+    ins = to_dev(workloads.make_inputs(w), cuda_device)
+    from expertscattergather_b200.step import train_step
+    train_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])      # warm the allocator and the library
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    out = train_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    outputs = sum(v.numel() * v.element_size() for v in out.values())
+    scratch = 2 * w.E * w.I * w.J * 4
+    gathered_block = w.B * w.E * w.K * w.I * 2
+    assert peak <= outputs + scratch + (1 << 20), (peak, outputs, scratch)
+    assert gathered_block > (1 << 22)     # the block the reference's torch path materialises would be visible
