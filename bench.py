@@ -145,7 +145,7 @@ def run_reference_arm(args, name, passes):
     base["value"] = v
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.median(x[1] for x in vals) * 1e3,
-            "higher_is_better": True, "scaling": "strong" if name == "cfg4" else "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if name.startswith("cfg4") else "weak", "vs_baseline": None,
             "dtype": str(passes[0].dtype).replace("torch.", ""), "data": "synthetic",
             "config": {"workload": name, "device": "host CPU", "note": "torch restatement of egs/baselines.py; "
                        "each step is a bounded batch slice of the workload"},
@@ -179,6 +179,7 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--precision", default=None, choices=["strict", "tf32"])
+    ap.add_argument("--batch", type=int, default=None, help="override the global batch size B of the workload")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -186,6 +187,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     name, passes = resolve_workload(args.workload, args.gpus)
+    if args.batch is not None:
+        passes = [w.with_batch(args.batch) for w in passes]
+        name = f"{name} (B={args.batch})"
     if args.impl == "reference":
         run_reference_arm(args, name, passes)
         return
@@ -293,16 +297,32 @@ def main():
 
     # ---- per-operator timing on this stream -> dominant operator and its roofline ----
     def time_op(fn, reps):
-        for _ in range(3):
+        """Device time of one operator call (its kernels only): the call is captured into a CUDA graph so that
+        host launch overhead stays out of the events; L2 is flushed between repetitions."""
+        for _ in range(2):
             fn()
+        torch.cuda.synchronize()
+        g = None
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep = fn()   # noqa: F841
+        except Exception:
+            g = None
+            torch.cuda.synchronize()
         ts = []
-        for _ in range(reps):
+        for _ in range(reps + 2):
             if flush_buf is not None:
                 flush_buf.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(); b.record(); b.synchronize()
+            a.record()
+            if g is not None:
+                g.replay()
+            else:
+                fn()
+            b.record(); b.synchronize()
             ts.append(a.elapsed_time(b))
-        return statistics.median(ts)
+        return statistics.median(ts[2:])
 
     breakdown = []
     reps = max(5, min(args.steps, 20))
@@ -408,7 +428,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if name == "cfg4" else "weak", "vs_baseline": None,
+            "scaling": "strong" if name.startswith("cfg4") else "weak", "vs_baseline": None,
             "dtype": {torch.float32: "f32 (tf32 tensor cores, %s)" % ops.get_precision(), torch.bfloat16: "bf16",
                       torch.float16: "f16"}[passes[0].dtype],
             "data": "synthetic",

@@ -23,7 +23,7 @@ STATUS_INDEX_OUT_OF_RANGE, STATUS_PIPELINE_TIMEOUT = 1, 2
 
 EXPORTS = (
     "egs_version", "egs_status_string", "egs_last_cuda_error", "egs_gather_gemm", "egs_gemm_scatter",
-    "egs_dweight", "egs_dw_workspace_bytes", "egs_tensor_path_eligible", "egs_fill_zero", "egs_launch_count",
+    "egs_dweight", "egs_dw_workspace_bytes", "egs_scatter_workspace_bytes", "egs_tensor_path_eligible", "egs_fill_zero", "egs_launch_count",
 )
 
 
@@ -46,7 +46,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_gather_gemm.restype = i
     lib.egs_gather_gemm.argtypes = [vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, vp, vp]
     lib.egs_gemm_scatter.restype = i
-    lib.egs_gemm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, i, vp, vp]
+    lib.egs_gemm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, i, vp, sz, vp, vp]
+    lib.egs_scatter_workspace_bytes.restype = sz
+    lib.egs_scatter_workspace_bytes.argtypes = [i64, i64, i64, i]
     lib.egs_dweight.restype = i
     lib.egs_dweight.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i, i, i, i, i, vp, sz, vp, vp]
     lib.egs_dw_workspace_bytes.restype = sz

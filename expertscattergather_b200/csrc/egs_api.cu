@@ -56,8 +56,8 @@ int check_dims(const egs_dims* d) {
 }
 
 int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, void* Out, const egs_dims* dims,
-                int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path, int32_t* status,
-                void* stream) {
+                int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path, void* workspace,
+                size_t workspace_bytes, int32_t* status, void* stream) {
   if (int rc = check_dims(dims)) return rc;
   if (!valid_dtype(dtype) || !valid_index(index_dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
       (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32) ||
@@ -72,21 +72,36 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   const bool no_work = (d.B * d.E * d.K == 0);
   if (!no_work && (!A || !W || !Ind) && d.C > 0) return EGS_ERR_INVALID_ARGUMENT;
 
-  if (scatter && zero_output) {
+  // 16-bit scatter: contributions are summed in float32 scratch rows and rounded once at the end
+  const bool f32_rows = scatter && dtype != EGS_F32;
+  const size_t n_out = static_cast<size_t>(out_rows) * d.N;
+  float* acc = nullptr;
+  if (f32_rows) {
+    if (!workspace || workspace_bytes < n_out * sizeof(float) || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
+    acc = static_cast<float*>(workspace);
+    cudaError_t err = zero_output ? launch_fill_zero(acc, n_out * sizeof(float), st)
+                                  : launch_convert_to_f32(Out, acc, n_out, dtype, st);
+    if (err != cudaSuccess) return fail_cuda(err, "scatter scratch init");
+  } else if (scatter && zero_output) {
     cudaError_t err = launch_fill_zero(Out, out_bytes, st);
     if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
   }
-  if (no_work) return EGS_OK;
+  auto finish_rows = [&]() -> int {
+    if (!f32_rows) return EGS_OK;
+    cudaError_t err = launch_convert_from_f32(acc, Out, n_out, dtype, st);
+    return err == cudaSuccess ? EGS_OK : fail_cuda(err, "scatter scratch convert");
+  };
+  if (no_work) return finish_rows();
   if (d.C == 0) {   // empty contraction: gather output is all zeros, scatter adds nothing
     if (!scatter) {
       cudaError_t err = launch_fill_zero(Out, out_bytes, st);
       if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
     }
-    return EGS_OK;
+    return finish_rows();
   }
 
   RowGemmParams p{};
-  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.status = status;
+  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.acc = acc; p.status = status;
   p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
   p.C = static_cast<int>(d.C); p.N = static_cast<int>(d.N);
   p.M = static_cast<int>(d.B * d.K);
@@ -103,7 +118,7 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     err = launch_generic_rowgemm(p, scatter, dtype, st);
   }
   if (err != cudaSuccess) return fail_cuda(err, scatter ? "gemm_scatter launch" : "gather_gemm launch");
-  return EGS_OK;
+  return finish_rows();
 }
 
 }  // namespace
@@ -133,15 +148,20 @@ int64_t egs_launch_count(void) { return g_launches.load(std::memory_order_relaxe
 
 int egs_gather_gemm(const void* X, const void* W, const void* Ind, void* Y, const egs_dims* dims, int w_layout,
                     int dtype, int index_dtype, int precision, int path, int32_t* status_word, void* cuda_stream) {
-  return run_rowgemm(false, X, W, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, status_word,
-                     cuda_stream);
+  return run_rowgemm(false, X, W, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, nullptr, 0,
+                     status_word, cuda_stream);
 }
 
 int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, const egs_dims* dims, int w_layout,
-                     int zero_output, int dtype, int index_dtype, int precision, int path, int32_t* status_word,
-                     void* cuda_stream) {
-  return run_rowgemm(true, Y, W, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path,
-                     status_word, cuda_stream);
+                     int zero_output, int dtype, int index_dtype, int precision, int path, void* workspace,
+                     size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  return run_rowgemm(true, Y, W, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path, workspace,
+                     workspace_bytes, status_word, cuda_stream);
+}
+
+size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype) {
+  if (dtype == EGS_F32 || B <= 0 || T <= 0 || N <= 0) return 0;
+  return static_cast<size_t>(B) * T * N * sizeof(float);
 }
 
 size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype) {

@@ -110,7 +110,8 @@ __global__ void __launch_bounds__(NTHREADS) generic_rowgemm_kernel(RowGemmParams
       const int nn = n0 + tx * 4 + j;
       if (nn >= p.N) continue;
       if (SCATTER) {
-        atomicAdd(Out + ro + nn, from_f32<T>(acc[i][j]));
+        if (sizeof(T) == 2) atomicAdd(p.acc + ro + nn, acc[i][j]);   // 16-bit: float32 accumulation rows
+        else atomicAdd(reinterpret_cast<float*>(Out) + ro + nn, acc[i][j]);
       } else {
         Out[ro + nn] = from_f32<T>(acc[i][j]);
       }
@@ -231,6 +232,14 @@ __global__ void __launch_bounds__(256) convert_from_f32_kernel(const float* __re
     dst[i] = from_f32<T>(src[i]);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) convert_to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst,
+                                                            size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = to_f32<T>(src[i]);
+}
+
 int grid_for(size_t work_items, int per_block) {
   size_t blocks = (work_items + per_block - 1) / per_block;
   const size_t cap = 148 * 8;   // a few waves of the 148 SMs; the kernels use grid-stride loops
@@ -287,6 +296,17 @@ cudaError_t launch_convert_from_f32(const float* src, void* dst, size_t n, int d
   if (dtype == EGS_F16) convert_from_f32_kernel<__half><<<grid, 256, 0, st>>>(src, static_cast<__half*>(dst), n);
   else if (dtype == EGS_BF16)
     convert_from_f32_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  else return cudaErrorInvalidValue;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_convert_to_f32(const void* src, float* dst, size_t n, int dtype, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  const int grid = grid_for(n, 256 * 4);
+  if (dtype == EGS_F16) convert_to_f32_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), dst, n);
+  else if (dtype == EGS_BF16)
+    convert_to_f32_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(src), dst, n);
   else return cudaErrorInvalidValue;
   count_launch();
   return cudaGetLastError();

@@ -44,6 +44,7 @@ struct RowGemmParams {
   const void* W;      // [E, C, N] (EGS_W_CN) or [E, N, C] (EGS_W_NC)
   const void* Ind;    // [B, E, K]
   void* Out;          // G: slot rows [B*E*K, N]     S: token rows [B*T, N]
+  float* acc;         // S with 16-bit tensors: float32 accumulation rows [B*T, N]; otherwise unused
   int32_t* status;    // optional device status word
   int B, T, E, K, C, N;
   int M;              // expert rows per expert = B*K
@@ -77,6 +78,7 @@ cudaError_t launch_generic_rowgemm(const RowGemmParams& p, bool scatter, int dty
 cudaError_t launch_generic_dweight(const DWeightParams& p, int dtype, cudaStream_t st);
 cudaError_t launch_fill_zero(void* ptr, size_t bytes, cudaStream_t st);
 cudaError_t launch_convert_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t st);
+cudaError_t launch_convert_to_f32(const void* src, float* dst, size_t n, int dtype, cudaStream_t st);
 
 // Tensor-core (tcgen05) family.  `configure_*` fills BN/stages and returns the dynamic shared memory size.
 size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision);

@@ -4,7 +4,7 @@
 //   warps 0..7  producers: index-driven 16-byte cp.async row gathers from global memory into shared
 //               memory, written directly in the 128-byte-swizzled layout the tensor core reads, through a
 //               ring of `stages` buffers; afterwards the same warps run the epilogue (tcgen05.ld of the
-//               accumulator, then vector stores or vector red.global.add into the destination rows)
+//               accumulator, then vector stores or vector red.global.add.f32 into the destination rows)
 //   warp 8      allocates tensor memory; one lane issues tcgen05.mma per stage and commits to mbarriers
 // Stage hand-over uses mbarriers only (full[s]: producers -> MMA lane, empty[s]: MMA completion ->
 // producers, done: all MMAs -> epilogue).  Every wait is bounded: when it runs out the thread sets the
@@ -20,6 +20,9 @@
 // descriptor (rows = contraction index, LBO = seg_stride, SBO = 1024) the same bytes are a transposed
 // operand.  That is what lets gathered rows feed both  rows x W  (operators G, S) and  rows^T x rows
 // (operator D) without a transposing copy, and never materialises the gathered [B,E,K,I] block.
+// One exception: the tensor core reads MN-major 32-bit (TF32) operands only in the variant of this format
+// whose XOR acts on 32-byte pairs with the row index modulo 4 (atoms of 4 rows; SBO = 512); float32 tiles
+// that are consumed MN-major are written in that variant.
 //
 // float32 tensors: kind::tf32.  EGS_PREC_STRICT splits every operand chunk in shared memory into
 // hi = top 19 bits and lo = tf32(x - hi) and issues lo*hi + hi*lo + hi*hi into the same accumulator, which
@@ -148,14 +151,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor, sm_100 version field set.  layout_type 2 = 128-byte swizzle (16-byte
+// granules, 8-row atoms); 1 = 128-byte swizzle with 32-byte granules and 4-row atoms, the only layout the
+// tensor core accepts for MN-major (transposed) 32-bit operands.
+constexpr uint32_t kSwizzle128 = 2, kSwizzle128Base32 = 1;
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type = kSwizzle128) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;   // descriptor version of this architecture
-  d |= static_cast<uint64_t>(2) << 61;   // layout type: 128-byte swizzle
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 // Instruction descriptor: fp32 accumulator, A and B of one format (0 f16, 1 bf16, 2 tf32).
@@ -166,9 +173,13 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t a_mn_major
 }
 
 // Address of (row r, 16-byte chunk c) inside a tile in the format described at the top of the file.
+// BASE32 selects the 32-byte-granule swizzle: rows stay 128 bytes apart, but the XOR acts on the 32-byte
+// pair index with the row index modulo 4 (atoms of 4 rows, 512 bytes).
+template <bool BASE32>
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, uint32_t seg_stride, int r, int c) {
-  return base + static_cast<uint32_t>(c >> 3) * seg_stride + static_cast<uint32_t>(r >> 3) * 1024u +
-         static_cast<uint32_t>(r & 7) * 128u + (static_cast<uint32_t>((c & 7) ^ (r & 7)) << 4);
+  const uint32_t row = base + static_cast<uint32_t>(c >> 3) * seg_stride + static_cast<uint32_t>(r) * 128u;
+  if (BASE32) return row + (static_cast<uint32_t>(((c & 7) >> 1) ^ (r & 3)) << 5) + (static_cast<uint32_t>(c & 1) << 4);
+  return row + (static_cast<uint32_t>((c & 7) ^ (r & 7)) << 4);
 }
 
 // In-place hi/lo split of one 16-byte chunk of float32 values (strict mode).
@@ -225,25 +236,6 @@ __device__ __forceinline__ void red_vec(float* dst, const uint32_t (&r)[16], int
                    "f"(__uint_as_float(r[v * 4 + 3]))
                    : "memory");
 }
-__device__ __forceinline__ void red_vec(__nv_bfloat16* dst, const uint32_t (&r)[16], int nvalid) {
-#pragma unroll
-  for (int v = 0; v < 2; ++v)
-    if (v * 8 < nvalid)
-      asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 8),
-                   "r"(pack2(dst, r[v * 8], r[v * 8 + 1])), "r"(pack2(dst, r[v * 8 + 2], r[v * 8 + 3])),
-                   "r"(pack2(dst, r[v * 8 + 4], r[v * 8 + 5])), "r"(pack2(dst, r[v * 8 + 6], r[v * 8 + 7]))
-                   : "memory");
-}
-__device__ __forceinline__ void red_vec(__half* dst, const uint32_t (&r)[16], int nvalid) {
-#pragma unroll
-  for (int v = 0; v < 2; ++v)
-    if (v * 8 < nvalid)
-      asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 8),
-                   "r"(pack2(dst, r[v * 8], r[v * 8 + 1])), "r"(pack2(dst, r[v * 8 + 2], r[v * 8 + 3])),
-                   "r"(pack2(dst, r[v * 8 + 4], r[v * 8 + 5])), "r"(pack2(dst, r[v * 8 + 6], r[v * 8 + 7]))
-                   : "memory");
-}
-
 __device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
   uint32_t c = 32;
   while (c < static_cast<uint32_t>(bn)) c <<= 1;
@@ -266,6 +258,9 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
   constexpr int ES = sizeof(T);
   constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
   constexpr int UK = 32 / ES;         // contraction elements per tcgen05.mma
+  constexpr bool kMn32 = (ES == 4);   // MN-major 32-bit tiles use the 32-byte-granule swizzle
+  constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
+  constexpr uint32_t kMnSbo = kMn32 ? 512u : 1024u;
   extern __shared__ unsigned char smem_raw[];
   char* smem = aligned_smem(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
@@ -353,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
           const int r = (tid >> 3) + 32 * i;
           const int ra = hdr->row_a[r];
           const bool v = kvalid && ra >= 0;
-          f(tile_addr(stage_base, 0u, r, cc), v ? A + static_cast<long long>(ra) * row_bytes_a + koff : A, v, false);
+          f(tile_addr<false>(stage_base, 0u, r, cc), v ? A + static_cast<long long>(ra) * row_bytes_a + koff : A, v, false);
         }
       }
       if (w_nc) {   // B rows = n (BN rows x 8 chunks), contraction contiguous
@@ -363,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
         for (int r = tid >> 3; r < p.BN; r += kProducerThreads / 8) {
           const bool v = kvalid && (n0 + r) < p.N;
           const char* src = W + (static_cast<long long>(e) * p.N + n0 + r) * row_bytes_a + koff;
-          f(tile_addr(stage_base + b_off, 0u, r, cc), v ? src : W, v, true);
+          f(tile_addr<false>(stage_base + b_off, 0u, r, cc), v ? src : W, v, true);
         }
       } else {      // B rows = contraction index (KE rows x nseg_b*8 chunks), n contiguous
         const int cpr = nseg_b * 8;
@@ -374,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
           const long long noff = noff0 + c * 16;
           const bool v = (k0 + r) < p.C && noff < row_bytes_w;
           const char* src = W + (static_cast<long long>(e) * p.C + k0 + r) * row_bytes_w + noff;
-          f(tile_addr(stage_base + b_off, KE * 128u, r, c), v ? src : W, v, true);
+          f(tile_addr<kMn32>(stage_base + b_off, KE * 128u, r, c), v ? src : W, v, true);
         }
       }
     };
@@ -430,9 +425,13 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = 0u;
           }
-          T* dst = out + static_cast<long long>(ro) * p.N + col;
-          if (SCATTER) red_vec(dst, v, nvalid);
-          else store_vec(dst, v, nvalid);
+          const long long off = static_cast<long long>(ro) * p.N + col;
+          if (SCATTER) {
+            if (ES == 2) red_vec(p.acc + off, v, nvalid);                       // 16-bit: float32 accumulation rows
+            else red_vec(reinterpret_cast<float*>(out) + off, v, nvalid);
+          } else {
+            store_vec(out + off, v, nvalid);
+          }
         }
       }
     }
@@ -456,10 +455,12 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
           const uint32_t b_k = w_nc ? kq * 32u : kq * (UK * 128u);
           const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
           const uint64_t ad = make_smem_desc(a_hi + a_k, 16u, 1024u);
-          const uint64_t bd = make_smem_desc(b_hi + b_k, b_lbo, 1024u);
+          const uint32_t b_sbo = w_nc ? 1024u : kMnSbo;
+          const uint32_t b_lay = w_nc ? kSwizzle128 : kMnLayout;
+          const uint64_t bd = make_smem_desc(b_hi + b_k, b_lbo, b_sbo, b_lay);
           if (STRICT) {
             const uint64_t adl = make_smem_desc(a_hi + a_lo_off + a_k, 16u, 1024u);
-            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + b_k, b_lbo, 1024u);
+            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + b_k, b_lbo, b_sbo, b_lay);
             umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
             umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
@@ -495,6 +496,9 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
   constexpr int UK = 32 / ES;           // contraction rows per tcgen05.mma
   constexpr int NSEG_A = ES;            // 128 features * ES bytes / 128
   constexpr int CPR_A = NSEG_A * 8;     // 16-byte chunks per A row
+  constexpr bool kMn32 = (ES == 4);     // MN-major 32-bit tiles use the 32-byte-granule swizzle
+  constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
+  constexpr uint32_t kMnSbo = kMn32 ? 512u : 1024u;
   extern __shared__ unsigned char smem_raw[];
   char* smem = aligned_smem(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
@@ -571,7 +575,7 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
             atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
           }
         }
-        f(tile_addr(stage_base, seg_stride, r, c), src, v, false);
+        f(tile_addr<kMn32>(stage_base, seg_stride, r, c), src, v, false);
       }
       // B: KR contraction rows x cpr_b chunks of the BN direct features
       for (int idx = tid; idx < KR * cpr_b; idx += kProducerThreads) {
@@ -585,7 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
           v = true;
           src = Ys + (static_cast<long long>(b * p.E + e) * p.K + k) * row_bytes_d + goff;
         }
-        f(tile_addr(stage_base + b_off, seg_stride, r, c), src, v, true);
+        f(tile_addr<kMn32>(stage_base + b_off, seg_stride, r, c), src, v, true);
       }
     };
 
@@ -671,11 +675,11 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
           const uint32_t koff = kq * (UK * 128u);
-          const uint64_t ad = make_smem_desc(a_hi + koff, seg_stride, 1024u);
-          const uint64_t bd = make_smem_desc(b_hi + koff, seg_stride, 1024u);
+          const uint64_t ad = make_smem_desc(a_hi + koff, seg_stride, kMnSbo, kMnLayout);
+          const uint64_t bd = make_smem_desc(b_hi + koff, seg_stride, kMnSbo, kMnLayout);
           if (STRICT) {
-            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + koff, seg_stride, 1024u);
-            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + koff, seg_stride, 1024u);
+            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + koff, seg_stride, kMnSbo, kMnLayout);
+            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + koff, seg_stride, kMnSbo, kMnLayout);
             umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
             umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);

@@ -193,8 +193,11 @@ def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=
                 raise ValueError("out must be a contiguous [B,T,N] tensor of Y's dtype")
             zero = 0
         dims = _lib.Dims(B, T, E, K, C, N)
+        ws_bytes = int(lib.egs_scatter_workspace_bytes(B, T, N, dt))
+        ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if ws_bytes else None
         rc = lib.egs_gemm_scatter(Yc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl,
-                                  zero, dt, it, prec, pth, _status_word(dev).data_ptr(), _stream_ptr(dev))
+                                  zero, dt, it, prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
+                                  _status_word(dev).data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "egs_gemm_scatter")
     if _state["debug"]:
         check_status(dev)

@@ -45,7 +45,7 @@ def test_argument_validation_needs_no_gpu():
     d = _lib.Dims(1, 1, 1, 1, 4, 4)
     assert lib.egs_gather_gemm(None, None, None, None, ctypes.byref(d), 7, 0, 0, 0, 0, None, None) == \
         _lib.ERR_INVALID_ARGUMENT
-    assert lib.egs_gemm_scatter(None, None, None, None, ctypes.byref(d), 0, 1, 9, 0, 0, 0, None, None) == \
+    assert lib.egs_gemm_scatter(None, None, None, None, ctypes.byref(d), 0, 1, 9, 0, 0, 0, None, 0, None, None) == \
         _lib.ERR_INVALID_ARGUMENT
     neg = _lib.Dims(-1, 1, 1, 1, 4, 4)
     assert lib.egs_gather_gemm(None, None, None, None, ctypes.byref(neg), 0, 0, 0, 0, 0, None, None) == \
@@ -68,3 +68,5 @@ def test_workspace_size_rule():
     assert lib.egs_dw_workspace_bytes(4, 8, 16, _lib.F32) == 0
     assert lib.egs_dw_workspace_bytes(4, 8, 16, _lib.BF16) == 4 * 8 * 16 * 4
     assert lib.egs_dw_workspace_bytes(0, 8, 16, _lib.BF16) == 0
+    assert lib.egs_scatter_workspace_bytes(2, 8, 16, _lib.F32) == 0
+    assert lib.egs_scatter_workspace_bytes(2, 8, 16, _lib.F16) == 2 * 8 * 16 * 4
