@@ -217,10 +217,7 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, 
     p.rows_per_split = static_cast<int>(rows);
     p.splits = static_cast<int>((p.M + rows - 1) / rows);
   }
-  if (static_cast<long long>(p.E) * p.splits > 65535) {   // grid.z limit: fall back to fewer splits
-    p.splits = 1;
-    p.rows_per_split = (p.M + 127) / 128 * 128;
-  }
+  if (static_cast<long long>(p.E) * p.splits > 65535) return EGS_ERR_TOO_LARGE;   // grid.z limit
 
   cudaError_t err;
   if (p.splits > 1) {

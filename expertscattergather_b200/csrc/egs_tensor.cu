@@ -6,10 +6,14 @@
 //               ring of `stages` buffers; afterwards the same warps run the epilogue (tcgen05.ld of the
 //               accumulator, then vector stores or vector red.global.add.f32 into the destination rows)
 //   warp 8      allocates tensor memory; one lane issues tcgen05.mma per stage and commits to mbarriers
-// Stage hand-over uses mbarriers only (full[s]: producers -> MMA lane, empty[s]: MMA completion ->
-// producers, done: all MMAs -> epilogue).  Every wait is bounded: when it runs out the thread sets the
-// CTA's abort flag and EGS_STATUS_PIPELINE_TIMEOUT in the caller's status word, and all roles fall through
-// to the common exit, where tensor memory is released.
+// Stage hand-over uses mbarriers only: empty[s] (MMA completion -> producers), full[s] (data landed ->
+// MMA lane), done (all MMAs -> epilogue).  Producers never wait for their own copies: after issuing a
+// stage each thread executes cp.async.mbarrier.arrive.noinc, so the hardware arrives on full[s] when that
+// thread's copies have landed and the producers run ahead by the whole ring.  (Strict float32 is the
+// exception: it must pass the landed data through registers to split it, so there the producers wait for
+// the copy group, split in place and arrive themselves.)  Every wait is bounded: when it runs out the
+// thread sets the CTA's abort flag and EGS_STATUS_PIPELINE_TIMEOUT in the caller's status word, and all
+// roles fall through to the common exit, where tensor memory is released.
 //
 // Shared-memory tile format (one format for every operand): rows of 128-byte segments.  Element
 // (row r, 16-byte chunk c of the row) lives at
@@ -28,6 +32,8 @@
 // hi = top 19 bits and lo = tf32(x - hi) and issues lo*hi + hi*lo + hi*hi into the same accumulator, which
 // restores ~fp32 product accuracy (the reference computes fp32 dots with allow_tf32=False,
 // egs/triton_kernels.py:389).  16-bit tensors: kind::f16 with fp32 accumulation.
+#include <cstdlib>
+
 #include "egs_internal.cuh"
 
 namespace egs {
@@ -38,10 +44,11 @@ constexpr int kProducerWarps = 8;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kThreads = kProducerThreads + 32;
 constexpr int kTileM = 128;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 constexpr uint32_t kHeaderBytes = 2048;
-constexpr size_t kSmemBudget = 200 * 1024;
 constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 clocks
+
+constexpr int kMaxRowsPerSplit = 4096;   // operator D: contraction rows one CTA may own (row table in smem)
 
 struct __align__(16) SmemHeader {
   unsigned long long full[kMaxStages];
@@ -63,13 +70,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+// Hardware arrive on an mbarrier once all cp.async copies this thread has issued so far have landed.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_pending(int n) {
   switch (n) {
     case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
     case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
     case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
   }
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -108,6 +123,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+
+// One lane polls, the warp shares the outcome (keeps 31 lanes per warp off the barrier word).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               int32_t* status, int lane) {
+  uint32_t ok = 1u;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -248,13 +271,122 @@ __device__ __forceinline__ char* aligned_smem(unsigned char* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Pipeline pieces shared by the two kernels
+// ------------------------------------------------------------------------------------------------
+struct Pipe {
+  SmemHeader* hdr;
+  volatile uint32_t* abort_flag;
+  int32_t* status;
+  uint32_t tiles0;        // shared-window address of stage 0
+  uint32_t stage_bytes;
+  int stages;
+  int nk;                 // stages of work (contraction steps)
+};
+
+// One CTA-wide barrier: mbarrier init, abort check, tensor-memory allocation.  Returns the TMEM base.
+__device__ __forceinline__ uint32_t pipe_setup(const Pipe& pp, uint32_t full_count, uint32_t tmem_cols, int tid, int warp) {
+  SmemHeader* hdr = pp.hdr;
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), full_count);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&hdr->done), 1);
+    fence_mbar_init();
+    // A launch that follows a timed-out one on the same status word does no work (keeps a broken pipeline
+    // from costing one wait limit per wave of CTAs).
+    hdr->abort_flag =
+        (pp.status && (*reinterpret_cast<volatile int32_t*>(pp.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+  }
+  if (warp == kProducerWarps) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  return hdr->tmem_base;
+}
+
+__device__ __forceinline__ void pipe_teardown(uint32_t tmem_base, uint32_t tmem_cols, int warp) {
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// Producer main loop.  issue(kt, stage_base) enqueues this thread's cp.async copies of stage kt;
+// split(kt, stage_base) is the strict-mode in-place hi/lo pass over the same chunks.
+template <bool STRICT, class Issue, class Split>
+__device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& issue, Split&& split) {
+  SmemHeader* hdr = pp.hdr;
+  const int stages = pp.stages, nk = pp.nk;
+  bool alive = true;
+  if (!STRICT) {
+    for (int kt = 0; kt < nk; ++kt) {
+      const int slot = kt % stages, use = kt / stages;
+      if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
+      if (!alive) break;
+      issue(kt, pp.tiles0 + slot * pp.stage_bytes);
+      cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
+    }
+  } else {
+    const int dist = stages - 1;
+    for (int kt = 0; kt < dist; ++kt) {
+      if (kt < nk) issue(kt, pp.tiles0 + (kt % stages) * pp.stage_bytes);
+      cp_async_commit();
+    }
+    for (int kc = 0; kc < nk; ++kc) {
+      cp_async_wait_pending(dist - 1);
+      if (alive) {
+        split(kc, pp.tiles0 + (kc % stages) * pp.stage_bytes);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
+      }
+      const int kt = kc + dist;
+      if (kt < nk && alive) {
+        const int use = kt / stages;
+        if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[kt % stages]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
+        if (alive) issue(kt, pp.tiles0 + (kt % stages) * pp.stage_bytes);
+      }
+      cp_async_commit();
+    }
+  }
+  cp_async_wait_all();
+  // all lanes of a warp must take the tcgen05.ld of the epilogue together: the decision is warp-uniform
+  alive = __all_sync(0xffffffffu, alive);
+  if (alive && nk > 0) alive = mbar_wait_warp(smem_u32(&hdr->done), 0u, pp.abort_flag, pp.status, lane);
+  if (alive) tc_fence_after();
+  return alive;
+}
+
+// MMA lane main loop.  mma(ks, stage_base) issues the tcgen05.mma instructions of stage ks.
+template <class Mma>
+__device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
+  SmemHeader* hdr = pp.hdr;
+  bool ok = true;
+  for (int ks = 0; ks < pp.nk; ++ks) {
+    const int slot = ks % pp.stages;
+    ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / pp.stages) & 1, pp.abort_flag, pp.status);
+    if (!ok) break;
+    tc_fence_after();
+    mma(ks, pp.tiles0 + slot * pp.stage_bytes);
+    umma_commit(smem_u32(&hdr->empty[slot]));
+  }
+  if (ok && pp.nk > 0) umma_commit(smem_u32(&hdr->done));
+}
+
+// ------------------------------------------------------------------------------------------------
 // Operators G and S.   grid = (ceil(M/128), ceil(N/BN), E)
 //   A rows (K-major): G gathers token rows through Ind, S reads slot rows
 //   B = W[e]:  EGS_W_NC -> rows n, contraction contiguous (K-major);  EGS_W_CN -> rows c, n contiguous (MN-major)
-//   epilogue:  G stores slot rows;  S adds to token rows with vector red.global.add
+//   epilogue:  G stores slot rows;  S adds to token rows with vector red.global.add.f32
 // ------------------------------------------------------------------------------------------------
 template <typename T, bool STRICT, bool SCATTER>
-__global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmParams p) {
+__global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kernel(RowGemmParams p) {
   constexpr int ES = sizeof(T);
   constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
   constexpr int UK = 32 / ES;         // contraction elements per tcgen05.mma
@@ -264,33 +396,31 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
   extern __shared__ unsigned char smem_raw[];
   char* smem = aligned_smem(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
-  const uint32_t tiles0 = smem_u32(smem) + kHeaderBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = blockIdx.z;
   const int m0 = blockIdx.x * kTileM;
   const int n0 = blockIdx.y * p.BN;
   const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);       // MMA N of this tile (multiple of 16)
-  const int stages = p.stages;
   const bool w_nc = (p.w_layout == EGS_W_NC);
 
   const uint32_t a_bytes = kTileM * 128u;
   const int nseg_b = (p.BN * ES + 127) / 128;
   const uint32_t b_bytes = w_nc ? static_cast<uint32_t>(p.BN) * 128u : static_cast<uint32_t>(nseg_b) * KE * 128u;
-  const uint32_t stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
   const uint32_t a_lo_off = a_bytes;                                   // strict: A_hi | A_lo | B_hi | B_lo
   const uint32_t b_off = STRICT ? 2u * a_bytes : a_bytes;
   const uint32_t b_lo_off = b_bytes;
-  const int nk = (p.C + KE - 1) / KE;
-  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  Pipe pp;
+  pp.hdr = hdr;
+  pp.abort_flag = &hdr->abort_flag;
+  pp.status = p.status;
+  pp.tiles0 = smem_u32(smem) + kHeaderBytes;
+  pp.stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
+  pp.stages = p.stages;
+  pp.nk = (p.C + KE - 1) / KE;
 
   // ---- set-up ----
-  // A launch that follows a timed-out one on the same status word does no work (keeps a broken pipeline
-  // from costing one wait limit per wave of CTAs).
-  if (tid == 0)
-    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
-  __syncthreads();
-  if (hdr->abort_flag) return;
   if (tid < kTileM) {
     const int m = m0 + tid;
     int ra = -1, ro = -1;
@@ -304,37 +434,23 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
         ro = SCATTER ? tok : slot;
       } else {
         if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
-        if (!SCATTER) ro = slot;
+        if (!SCATTER) ro = slot;      // gather: the row is still written (zeros)
       }
     }
     hdr->row_a[tid] = ra;
     hdr->row_o[tid] = ro;
   }
-  if (tid == 0) {
-    for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(smem_u32(&hdr->full[s]), kProducerWarps);
-      mbar_init(smem_u32(&hdr->empty[s]), 1);
-    }
-    mbar_init(smem_u32(&hdr->done), 1);
-    fence_mbar_init();
-  }
   const uint32_t tmem_cols = tmem_cols_for(p.BN);
-  if (warp == kProducerWarps) {
-    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = hdr->tmem_base;
+  const uint32_t tmem_base = pipe_setup(pp, STRICT ? kProducerWarps : kProducerThreads, tmem_cols, tid, warp);
+  const bool run = (hdr->abort_flag == 0u);
 
-  if (warp < kProducerWarps) {
+  if (!run) {
+    // fall through to the common exit
+  } else if (warp < kProducerWarps) {
     // =========================== producers ===========================
     const char* A = static_cast<const char*>(p.A);
     const char* W = static_cast<const char*>(p.W);
     const long long row_bytes_a = static_cast<long long>(p.C) * ES;
-    const int dist = stages - 1;
-    bool alive = true;
 
     // visits every 16-byte chunk this thread owns in stage `kt`:  f(dst_hi_addr, src, valid, is_b)
     auto for_each_chunk = [&](int kt, uint32_t stage_base, auto&& f) {
@@ -373,45 +489,22 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
         }
       }
     };
-
-    for (int kt = 0; kt < nk + dist; ++kt) {
-      if (kt < nk && alive) {
-        const int slot = kt % stages, use = kt / stages;
-        if (use > 0) alive = mbar_wait(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status);
-        if (alive) {
-          for_each_chunk(kt, tiles0 + slot * stage_bytes,
-                         [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
-        }
-      }
-      cp_async_commit();
-      const int kc = kt - dist;
-      if (kc >= 0) {
-        cp_async_wait_pending(dist);
-        if (alive) {
-          if (STRICT) {
-            const int slot = kc % stages;
-            for_each_chunk(kc, tiles0 + slot * stage_bytes, [&](uint32_t dst, const char*, bool, bool is_b) {
-              split_chunk(dst, is_b ? b_lo_off : a_lo_off);
-            });
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
-        }
-      }
-    }
-    cp_async_wait_pending(0);
+    const bool alive = run_producer<STRICT>(
+        pp, lane,
+        [&](int kt, uint32_t base) {
+          for_each_chunk(kt, base, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
+        },
+        [&](int kc, uint32_t base) {
+          for_each_chunk(kc, base, [&](uint32_t dst, const char*, bool, bool is_b) {
+            split_chunk(dst, is_b ? b_lo_off : a_lo_off);
+          });
+        });
 
     // =========================== epilogue ===========================
-    if (alive) alive = mbar_wait(smem_u32(&hdr->done), 0u, abort_flag, p.status);
-    // all lanes of a warp must take the tcgen05.ld together: make the decision warp-uniform
-    alive = __all_sync(0xffffffffu, alive);
     if (alive) {
-      tc_fence_after();
       const int lg = warp & 3, half = warp >> 2;
       const int r = lg * 32 + lane;
       const int ro = hdr->row_o[r];
-      const bool zero_row = (!SCATTER) && hdr->row_a[r] < 0;   // gather: masked source row -> zeros
       T* out = static_cast<T*>(p.Out);
       const int nch = bn >> 4;
       for (int c = half; c < nch; c += 2) {
@@ -421,16 +514,12 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
         const int col = n0 + c * 16;
         const int nvalid = min(16, p.N - col);
         if (ro >= 0 && nvalid > 0) {
-          if (zero_row) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = 0u;
-          }
           const long long off = static_cast<long long>(ro) * p.N + col;
           if (SCATTER) {
             if (ES == 2) red_vec(p.acc + off, v, nvalid);                       // 16-bit: float32 accumulation rows
             else red_vec(reinterpret_cast<float*>(out) + off, v, nvalid);
           } else {
-            store_vec(out + off, v, nvalid);
+            store_vec(out + off, v, nvalid);   // a masked source row was zero-filled in smem: zeros come out
           }
         }
       }
@@ -439,28 +528,21 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       const uint32_t idesc = make_idesc(Elem<T>::fmt, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(bn));
-      bool ok = true;
-      for (int ks = 0; ks < nk && ok; ++ks) {
-        const int slot = ks % stages;
-        ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / stages) & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t a_hi = tiles0 + slot * stage_bytes;
+      const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
+      const uint32_t b_sbo = w_nc ? 1024u : kMnSbo;
+      const uint32_t b_lay = w_nc ? kSwizzle128 : kMnLayout;
+      const uint32_t b_step = w_nc ? 32u : UK * 128u;
+      run_mma_lane(pp, [&](int ks, uint32_t a_hi) {
         const uint32_t b_hi = a_hi + b_off;
         const int krem = p.C - ks * KE;
         const int nkq = min(KE / UK, (krem + UK - 1) / UK);
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
-          const uint32_t a_k = kq * 32u;
-          const uint32_t b_k = w_nc ? kq * 32u : kq * (UK * 128u);
-          const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
-          const uint64_t ad = make_smem_desc(a_hi + a_k, 16u, 1024u);
-          const uint32_t b_sbo = w_nc ? 1024u : kMnSbo;
-          const uint32_t b_lay = w_nc ? kSwizzle128 : kMnLayout;
-          const uint64_t bd = make_smem_desc(b_hi + b_k, b_lbo, b_sbo, b_lay);
+          const uint64_t ad = make_smem_desc(a_hi + kq * 32u, 16u, 1024u);
+          const uint64_t bd = make_smem_desc(b_hi + kq * b_step, b_lbo, b_sbo, b_lay);
           if (STRICT) {
-            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + a_k, 16u, 1024u);
-            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + b_k, b_lbo, b_sbo, b_lay);
+            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + kq * 32u, 16u, 1024u);
+            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + kq * b_step, b_lbo, b_sbo, b_lay);
             umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
             umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
@@ -468,29 +550,22 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_rowgemm_kernel(RowGemmPara
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
           }
         }
-        umma_commit(smem_u32(&hdr->empty[slot]));
-      }
-      if (ok) umma_commit(smem_u32(&hdr->done));
+      });
     }
     __syncwarp();
   }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == kProducerWarps) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
+  pipe_teardown(tmem_base, tmem_cols, warp);
 }
 
 // ------------------------------------------------------------------------------------------------
 // Operator D.   grid = (ceil(FG/128), ceil(FD/BN), E*splits)
 //   accumulator tile P[f, g]: TMEM lane = f (feature of the gathered rows), column = g
 //   A = gathered token rows of Xsrc, B = slot rows of Ysrc; both consumed MN-major (rows = contraction)
+//   The token row of every contraction row this CTA owns is looked up once into a shared-memory table.
 //   splits == 1: the tile is stored in the output dtype; splits > 1: red.global.add.f32 into p.acc
 // ------------------------------------------------------------------------------------------------
 template <typename T, bool STRICT>
-__global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightParams p) {
+__global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kernel(DWeightParams p) {
   constexpr int ES = sizeof(T);
   constexpr int KR = 128 / ES;          // contraction rows per stage (4 MMAs of UK rows)
   constexpr int UK = 32 / ES;           // contraction rows per tcgen05.mma
@@ -502,7 +577,8 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
   extern __shared__ unsigned char smem_raw[];
   char* smem = aligned_smem(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
-  const uint32_t tiles0 = smem_u32(smem) + kHeaderBytes;
+  int* row_tok = reinterpret_cast<int*>(smem + kHeaderBytes);     // [rows_per_split] token row or -1
+  const uint32_t table_bytes = (static_cast<uint32_t>(p.rows_per_split) * 4u + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = blockIdx.z / p.splits;
@@ -510,129 +586,95 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
   const int f0 = blockIdx.x * kTileM;
   const int g0 = blockIdx.y * p.BN;
   const int bn = min(p.BN, ((p.FD - g0) + 15) & ~15);
-  const int stages = p.stages;
   const int m_begin = split * p.rows_per_split;
   const int m_end = min(p.M, m_begin + p.rows_per_split);
-  const int nk = (max(0, m_end - m_begin) + KR - 1) / KR;
+  const int rows = max(0, m_end - m_begin);
 
   const int nseg_b = (p.BN * ES + 127) / 128;
   const uint32_t seg_stride = KR * 128u;
   const uint32_t a_bytes = NSEG_A * seg_stride;
   const uint32_t b_bytes = static_cast<uint32_t>(nseg_b) * seg_stride;
-  const uint32_t stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
   const uint32_t a_lo_off = a_bytes;
   const uint32_t b_off = STRICT ? 2u * a_bytes : a_bytes;
   const uint32_t b_lo_off = b_bytes;
-  volatile uint32_t* abort_flag = &hdr->abort_flag;
 
-  if (tid == 0)
-    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
-  __syncthreads();
-  if (hdr->abort_flag) return;
-  if (tid == 0) {
-    for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(smem_u32(&hdr->full[s]), kProducerWarps);
-      mbar_init(smem_u32(&hdr->empty[s]), 1);
-    }
-    mbar_init(smem_u32(&hdr->done), 1);
-    fence_mbar_init();
+  Pipe pp;
+  pp.hdr = hdr;
+  pp.abort_flag = &hdr->abort_flag;
+  pp.status = p.status;
+  pp.tiles0 = smem_u32(smem) + kHeaderBytes + table_bytes;
+  pp.stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
+  pp.stages = p.stages;
+  pp.nk = (rows + KR - 1) / KR;
+
+  // ---- set-up: token-row table (coalesced reads of Ind), barriers, tensor memory ----
+  for (int i = tid; i < rows; i += kThreads) {
+    const int m = m_begin + i;
+    const int b = m / p.K, k = m - b * p.K;
+    const long long t = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + e) * p.K + k);
+    int tok = -1;
+    if (t >= 0 && t < p.T) tok = b * p.T + static_cast<int>(t);
+    else if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+    row_tok[i] = tok;
   }
   const uint32_t tmem_cols = tmem_cols_for(p.BN);
-  if (warp == kProducerWarps) {
-    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = hdr->tmem_base;
+  const uint32_t tmem_base = pipe_setup(pp, STRICT ? kProducerWarps : kProducerThreads, tmem_cols, tid, warp);
+  const bool run = (hdr->abort_flag == 0u);
 
-  if (warp < kProducerWarps) {
+  if (!run) {
+    // fall through to the common exit
+  } else if (warp < kProducerWarps) {
     const char* Xs = static_cast<const char*>(p.Xsrc);
     const char* Ys = static_cast<const char*>(p.Ysrc);
     const long long row_bytes_g = static_cast<long long>(p.FG) * ES;
     const long long row_bytes_d = static_cast<long long>(p.FD) * ES;
-    const int dist = stages - 1;
     const int cpr_b = nseg_b * 8;
-    bool alive = true;
 
-    auto for_each_chunk = [&](int kt, uint32_t stage_base, bool want_src, auto&& f) {
-      const int mrow0 = m_begin + kt * KR;
+    auto for_each_chunk = [&](int kt, uint32_t stage_base, auto&& f) {
+      const int i0 = kt * KR;
       // A: KR contraction rows x CPR_A chunks of the 128 gathered features
       for (int idx = tid; idx < KR * CPR_A; idx += kProducerThreads) {
         const int r = idx / CPR_A, c = idx % CPR_A;
-        const int m = mrow0 + r;
         const long long foff = static_cast<long long>(f0) * ES + c * 16;
-        bool v = false;
-        const char* src = Xs;
-        if (want_src && m < m_end && foff < row_bytes_g) {
-          const int b = m / p.K, k = m - b * p.K;
-          const long long t = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + e) * p.K + k);
-          if (t >= 0 && t < p.T) {
-            v = true;
-            src = Xs + (static_cast<long long>(b) * p.T + t) * row_bytes_g + foff;
-          } else if (p.status) {
-            atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
-          }
-        }
-        f(tile_addr<kMn32>(stage_base, seg_stride, r, c), src, v, false);
+        const int tok = (i0 + r < rows) ? row_tok[i0 + r] : -1;
+        const bool v = tok >= 0 && foff < row_bytes_g;
+        f(tile_addr<kMn32>(stage_base, seg_stride, r, c), v ? Xs + static_cast<long long>(tok) * row_bytes_g + foff : Xs, v,
+          false);
       }
       // B: KR contraction rows x cpr_b chunks of the BN direct features
       for (int idx = tid; idx < KR * cpr_b; idx += kProducerThreads) {
         const int r = idx / cpr_b, c = idx - r * cpr_b;
-        const int m = mrow0 + r;
+        const int m = m_begin + i0 + r;
         const long long goff = static_cast<long long>(g0) * ES + c * 16;
-        bool v = false;
+        const bool v = (i0 + r < rows) && goff < row_bytes_d;
         const char* src = Ys;
-        if (want_src && m < m_end && goff < row_bytes_d) {
+        if (v) {
           const int b = m / p.K, k = m - b * p.K;
-          v = true;
           src = Ys + (static_cast<long long>(b * p.E + e) * p.K + k) * row_bytes_d + goff;
         }
         f(tile_addr<kMn32>(stage_base + b_off, seg_stride, r, c), src, v, true);
       }
     };
-
-    for (int kt = 0; kt < nk + dist; ++kt) {
-      if (kt < nk && alive) {
-        const int slot = kt % stages, use = kt / stages;
-        if (use > 0) alive = mbar_wait(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status);
-        if (alive) {
-          for_each_chunk(kt, tiles0 + slot * stage_bytes, true,
-                         [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
-        }
-      }
-      cp_async_commit();
-      const int kc = kt - dist;
-      if (kc >= 0) {
-        cp_async_wait_pending(dist);
-        if (alive) {
-          if (STRICT) {
-            const int slot = kc % stages;
-            for_each_chunk(kc, tiles0 + slot * stage_bytes, false, [&](uint32_t dst, const char*, bool, bool is_b) {
-              split_chunk(dst, is_b ? b_lo_off : a_lo_off);
-            });
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
-        }
-      }
-    }
-    cp_async_wait_pending(0);
+    const bool alive = run_producer<STRICT>(
+        pp, lane,
+        [&](int kt, uint32_t base) {
+          for_each_chunk(kt, base, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, src, v ? 16u : 0u); });
+        },
+        [&](int kc, uint32_t base) {
+          for_each_chunk(kc, base, [&](uint32_t dst, const char*, bool, bool is_b) {
+            split_chunk(dst, is_b ? b_lo_off : a_lo_off);
+          });
+        });
 
     // epilogue
-    if (alive && nk > 0) alive = mbar_wait(smem_u32(&hdr->done), 0u, abort_flag, p.status);
-    alive = __all_sync(0xffffffffu, alive);
     if (alive) {
-      tc_fence_after();
       const int lg = warp & 3, half = warp >> 2;
       const int f = f0 + lg * 32 + lane;
       const int nch = bn >> 4;
       T* out = static_cast<T*>(p.out);
       for (int c = half; c < nch; c += 2) {
         uint32_t v[16];
-        if (nk > 0) {
+        if (pp.nk > 0) {
           tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
           tmem_ld_wait();
         } else {
@@ -662,15 +704,9 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
   } else {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(Elem<T>::fmt, 1u, 1u, kTileM, static_cast<uint32_t>(bn));
-      bool ok = true;
-      for (int ks = 0; ks < nk && ok; ++ks) {
-        const int slot = ks % stages;
-        ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / stages) & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t a_hi = tiles0 + slot * stage_bytes;
+      run_mma_lane(pp, [&](int ks, uint32_t a_hi) {
         const uint32_t b_hi = a_hi + b_off;
-        const int rrem = (m_end - m_begin) - ks * KR;
+        const int rrem = rows - ks * KR;
         const int nkq = min(KR / UK, (rrem + UK - 1) / UK);
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
@@ -687,25 +723,46 @@ __global__ void __launch_bounds__(kThreads, 1) tensor_dweight_kernel(DWeightPara
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
           }
         }
-        umma_commit(smem_u32(&hdr->empty[slot]));
-      }
-      if (ok && nk > 0) umma_commit(smem_u32(&hdr->done));
+      });
     }
     __syncwarp();
   }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == kProducerWarps) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
+  pipe_teardown(tmem_base, tmem_cols, warp);
 }
 
-int pick_stages(size_t stage_bytes) {
-  size_t s = (kSmemBudget - kHeaderBytes - 1024) / stage_bytes;
-  if (s > static_cast<size_t>(kMaxStages)) s = kMaxStages;
-  return static_cast<int>(s);
+// ------------------------------------------------------------------------------------------------
+// host side: tile / stage selection and launches
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kSmemPerSm = 228 * 1024;
+constexpr size_t kSmemReservedPerCta = 1024;
+constexpr size_t kSmemMaxPerCta = 227 * 1024;
+constexpr int kSmCount = 148;
+
+// Tuning aids (read once): EGS_B200_TILE_N caps the tile width over N (multiple of 16, 16..256);
+// EGS_B200_STAGES caps the pipeline depth (>= 2).
+int env_int(const char* name) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : 0;
+}
+int tile_n_cap(int dflt) {
+  static const int env = env_int("EGS_B200_TILE_N");
+  if (env >= 16 && env <= 256) return (env / 16) * 16 < dflt ? (env / 16) * 16 : dflt;
+  return dflt;
+}
+
+// Pipeline depth: large grids aim at two CTAs per SM (the prologue and epilogue of one CTA overlap the main
+// loop of the other); grids that fit in one wave take the whole SM.
+int pick_stages(size_t fixed_bytes, size_t stage_bytes, long long ctas, bool allow_two_per_sm) {
+  static const int env = env_int("EGS_B200_STAGES");
+  const size_t two = kSmemPerSm / 2 - kSmemReservedPerCta;
+  int s = 0;
+  if (allow_two_per_sm && ctas > kSmCount && fixed_bytes + 2 * stage_bytes <= two)
+    s = static_cast<int>((two - fixed_bytes) / stage_bytes);
+  else
+    s = static_cast<int>((kSmemMaxPerCta - fixed_bytes) / stage_bytes);
+  if (s > kMaxStages) s = kMaxStages;
+  if (env >= 2 && env < s) s = env;
+  return s;
 }
 
 }  // namespace
@@ -715,15 +772,17 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision) {
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int ke = 128 / es;
   int bn = (p.N + 15) & ~15;
-  const int cap = strict ? 128 : 256;
+  const int cap = tile_n_cap(strict ? 128 : 256);
   if (bn > cap) bn = cap;
   p.BN = bn;
   const size_t a_bytes = kTileM * 128;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t b_bytes = (p.w_layout == EGS_W_NC) ? static_cast<size_t>(bn) * 128 : nseg_b * ke * 128;
   const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
-  p.stages = pick_stages(stage_bytes);
-  return 1024 + kHeaderBytes + p.stages * stage_bytes;
+  const size_t fixed = 1024 + kHeaderBytes;
+  const long long ctas = static_cast<long long>((p.M + kTileM - 1) / kTileM) * ((p.N + bn - 1) / bn) * p.E;
+  p.stages = pick_stages(fixed, stage_bytes, ctas, !strict);
+  return fixed + p.stages * stage_bytes;
 }
 
 size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
@@ -731,17 +790,19 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int kr = 128 / es;
   int bn = (p.FD + 15) & ~15;
-  const int cap = strict ? 128 : 256;
+  const int cap = tile_n_cap(strict ? 128 : 256);
   if (bn > cap) bn = cap;
   p.BN = bn;
   const size_t seg_stride = static_cast<size_t>(kr) * 128;
   const size_t a_bytes = es * seg_stride;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t stage_bytes = (a_bytes + nseg_b * seg_stride) * (strict ? 2 : 1);
-  p.stages = pick_stages(stage_bytes);
-  // split the contraction so that the grid fills the 148 SMs about twice over
+  // split the contraction so that the grid covers the SMs about twice and no CTA owns more rows than the
+  // shared-memory row table holds
   const long long tiles = static_cast<long long>((p.FG + kTileM - 1) / kTileM) * ((p.FD + bn - 1) / bn) * p.E;
-  long long want = (2 * 148 + tiles - 1) / tiles;
+  long long want = (2 * kSmCount + tiles - 1) / tiles;
+  const long long min_splits = (p.M + kMaxRowsPerSplit - 1) / kMaxRowsPerSplit;
+  if (want < min_splits) want = min_splits;
   const long long max_splits = (p.M + kr - 1) / kr;
   if (want > max_splits) want = max_splits;
   if (want < 1) want = 1;
@@ -751,12 +812,23 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   p.rows_per_split = static_cast<int>(rows);
   p.splits = static_cast<int>((p.M + rows - 1) / rows);
   if (p.splits < 1) p.splits = 1;
-  return 1024 + kHeaderBytes + p.stages * stage_bytes;
+  const size_t table_bytes = (static_cast<size_t>(rows) * 4 + 1023) & ~static_cast<size_t>(1023);
+  const size_t fixed = 1024 + kHeaderBytes + table_bytes;
+  p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, !strict);
+  return fixed + p.stages * stage_bytes;
 }
 
-template <typename K>
-static cudaError_t set_smem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+// The opt-in to large dynamic shared memory is per kernel function: done once, for the maximum.
+template <auto kernel>
+static cudaError_t ensure_smem_optin() {
+  static thread_local int done_device = -1;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (done_device == dev) return cudaSuccess;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemMaxPerCta));
+  if (err == cudaSuccess) done_device = dev;
+  return err;
 }
 
 cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision, size_t smem_bytes,
@@ -767,10 +839,10 @@ cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtyp
 #define EGS_LAUNCH(TY, STRICT)                                                                  \
   do {                                                                                          \
     if (scatter) {                                                                              \
-      err = set_smem(tensor_rowgemm_kernel<TY, STRICT, true>, smem_bytes);                      \
+      err = (ensure_smem_optin<tensor_rowgemm_kernel<TY, STRICT, true>>());                        \
       if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, true><<<grid, block, smem_bytes, st>>>(p);  \
     } else {                                                                                    \
-      err = set_smem(tensor_rowgemm_kernel<TY, STRICT, false>, smem_bytes);                     \
+      err = (ensure_smem_optin<tensor_rowgemm_kernel<TY, STRICT, false>>());                        \
       if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, false><<<grid, block, smem_bytes, st>>>(p); \
     }                                                                                           \
   } while (0)
@@ -794,7 +866,7 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
   cudaError_t err = cudaSuccess;
 #define EGS_LAUNCH(TY, STRICT)                                                          \
   do {                                                                                  \
-    err = set_smem(tensor_dweight_kernel<TY, STRICT>, smem_bytes);                      \
+    err = (ensure_smem_optin<tensor_dweight_kernel<TY, STRICT>>());                        \
     if (err == cudaSuccess) tensor_dweight_kernel<TY, STRICT><<<grid, block, smem_bytes, st>>>(p); \
   } while (0)
   if (dtype == EGS_F32) {
