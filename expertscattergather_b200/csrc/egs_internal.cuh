@@ -52,6 +52,7 @@ struct RowGemmParams {
   int index_dtype;
   int BN;             // tensor path: tile width over N (multiple of 16, <= 256)
   int stages;         // tensor path: pipeline depth
+  int expert_fastest; // tensor path: grid order (1: experts vary fastest, row tiles slowest)
 };
 
 struct DWeightParams {

@@ -172,6 +172,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 consecutive fp32 accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, sm_100 version field set.  layout_type 2 = 128-byte swizzle (16-byte
@@ -226,13 +238,7 @@ template <> struct Elem<float> { static constexpr uint32_t fmt = 2; static const
 template <> struct Elem<__half> { static constexpr uint32_t fmt = 0; static constexpr bool tf32 = false; };
 template <> struct Elem<__nv_bfloat16> { static constexpr uint32_t fmt = 1; static constexpr bool tf32 = false; };
 
-// ---- epilogue helpers: 16 fp32 accumulator values -> destination row --------------------------------
-__device__ __forceinline__ void store_vec(float* dst, const uint32_t (&r)[16], int nvalid) {
-#pragma unroll
-  for (int v = 0; v < 4; ++v)
-    if (v * 4 < nvalid)
-      *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-}
+// ---- epilogue helpers ----
 __device__ __forceinline__ uint32_t pack2(__half*, uint32_t a, uint32_t b) {
   const __half2 h = __floats2half2_rn(__uint_as_float(a), __uint_as_float(b));
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -241,24 +247,53 @@ __device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, uint32_t a, uint32_t b
   const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
   return *reinterpret_cast<const uint32_t*>(&h);
 }
+// Warp-level transpose of a 32-row x 32-column fp32 accumulator block through a 4 KB shared-memory tile.
+// In tensor memory one thread owns one row, which would make every global access of a warp touch 32
+// different rows (16 bytes each).  After the transpose 8 lanes cover 128 contiguous bytes of one row, 4 rows
+// per instruction; for red.global.add that pattern measured ~3x the throughput of the row-per-thread one.
+//   emit(row_in_block, first_column, x0, x1, x2, x3) is called 8 times per lane.
+template <class Emit>
+__device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, int lane, bool have_acc, Emit&& emit) {
+  uint32_t v[32];
+  if (have_acc) {
+    tmem_ld32(taddr, v);
+    tmem_ld_wait();
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = 0u;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + lane * 128u + (static_cast<uint32_t>(j ^ (lane & 7)) << 4)),
+                 "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                 : "memory");
+  __syncwarp();
+  const int j = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    uint32_t x[4];
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3])
+                 : "r"(tile + row * 128u + (static_cast<uint32_t>(j ^ (row & 7)) << 4))
+                 : "memory");
+    emit(row, j * 4, x[0], x[1], x[2], x[3]);
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void red4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(__uint_as_float(x0)), "f"(__uint_as_float(x1)),
+               "f"(__uint_as_float(x2)), "f"(__uint_as_float(x3))
+               : "memory");
+}
+__device__ __forceinline__ void store4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(x0, x1, x2, x3);
+}
 template <typename T>
-__device__ __forceinline__ void store_vec(T* dst, const uint32_t (&r)[16], int nvalid) {
-#pragma unroll
-  for (int v = 0; v < 2; ++v)
-    if (v * 8 < nvalid)
-      *reinterpret_cast<uint4*>(dst + v * 8) =
-          make_uint4(pack2(dst, r[v * 8], r[v * 8 + 1]), pack2(dst, r[v * 8 + 2], r[v * 8 + 3]),
-                     pack2(dst, r[v * 8 + 4], r[v * 8 + 5]), pack2(dst, r[v * 8 + 6], r[v * 8 + 7]));
+__device__ __forceinline__ void store4(T* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+  *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(dst, x0, x1), pack2(dst, x2, x3));
 }
-__device__ __forceinline__ void red_vec(float* dst, const uint32_t (&r)[16], int nvalid) {
-#pragma unroll
-  for (int v = 0; v < 4; ++v)
-    if (v * 4 < nvalid)
-      asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + v * 4), "f"(__uint_as_float(r[v * 4])),
-                   "f"(__uint_as_float(r[v * 4 + 1])), "f"(__uint_as_float(r[v * 4 + 2])),
-                   "f"(__uint_as_float(r[v * 4 + 3]))
-                   : "memory");
-}
+
 __device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
   uint32_t c = 32;
   while (c < static_cast<uint32_t>(bn)) c <<= 1;
@@ -405,7 +440,10 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Operators G and S.   grid = (ceil(M/128), ceil(N/BN), E)
+// Operators G and S.   grid = (row tiles, ceil(N/BN), E), or with expert_fastest (E, ceil(N/BN), row tiles).
+//   Experts slowest: the CTAs in flight share one expert's weights and (for S) add to distinct token rows.
+//   Experts fastest: the CTAs in flight work on the same few batch elements, so the token rows they gather
+//   from or add to stay resident in L2 - chosen when those rows exceed L2 while all weights fit in it.
 //   A rows (K-major): G gathers token rows through Ind, S reads slot rows
 //   B = W[e]:  EGS_W_NC -> rows n, contraction contiguous (K-major);  EGS_W_CN -> rows c, n contiguous (MN-major)
 //   epilogue:  G stores slot rows;  S adds to token rows with vector red.global.add.f32
@@ -424,8 +462,8 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) EGS_MARK(0);
-  const int e = blockIdx.z;
-  const int m0 = blockIdx.x * kTileM;
+  const int e = p.expert_fastest ? blockIdx.x : blockIdx.z;
+  const int m0 = (p.expert_fastest ? blockIdx.z : blockIdx.x) * kTileM;
   const int n0 = blockIdx.y * p.BN;
   const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);       // MMA N of this tile (multiple of 16)
   const bool w_nc = (p.w_layout == EGS_W_NC);
@@ -553,27 +591,25 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
         });
 
     // =========================== epilogue ===========================
+    // The stage ring is idle once `done` has completed: its first 32 KB serve as the warps' transpose tiles.
     if (alive) {
       const int lg = warp & 3, half = warp >> 2;
-      const int r = lg * 32 + lane;
-      const int ro = hdr->row_o[r];
+      const uint32_t tile = pp.tiles0 + static_cast<uint32_t>(warp) * 4096u;
       T* out = static_cast<T*>(p.Out);
-      const int nch = bn >> 4;
-      for (int c = half; c < nch; c += 2) {
-        uint32_t v[16];
-        tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
-        tmem_ld_wait();
-        const int col = n0 + c * 16;
-        const int nvalid = min(16, p.N - col);
-        if (ro >= 0 && nvalid > 0) {
-          const long long off = static_cast<long long>(ro) * p.N + col;
-          if (SCATTER) {
-            if (ES == 2) red_vec(p.acc + off, v, nvalid);                       // 16-bit: float32 accumulation rows
-            else red_vec(reinterpret_cast<float*>(out) + off, v, nvalid);
-          } else {
-            store_vec(out + off, v, nvalid);   // a masked source row was zero-filled in smem: zeros come out
-          }
-        }
+      float* acc_rows = (ES == 2) ? p.acc : reinterpret_cast<float*>(p.Out);   // S: float32 rows being added to
+      const int nblk = (bn + 31) >> 5;
+      for (int c = half; c < nblk; c += 2) {
+        const int col0 = n0 + c * 32;
+        warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 32), tile, lane, true,
+                        [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                          const int ro = hdr->row_o[lg * 32 + row];
+                          const int col = col0 + cj;
+                          if (ro >= 0 && col < p.N) {
+                            const long long off = static_cast<long long>(ro) * p.N + col;
+                            if (SCATTER) red4(acc_rows + off, x0, x1, x2, x3);
+                            else store4(out + off, x0, x1, x2, x3);   // masked source rows were zero-filled: zeros
+                          }
+                        });
       }
     }
   } else {
@@ -752,26 +788,40 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
     // epilogue
     if (alive) {
       const int lg = warp & 3, half = warp >> 2;
-      const int f = f0 + lg * 32 + lane;
-      const int nch = bn >> 4;
       T* out = static_cast<T*>(p.out);
-      for (int c = half; c < nch; c += 2) {
-        uint32_t v[16];
-        if (pp.nk > 0) {
-          tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0u;
+      if (p.out_layout == EGS_DW_GATHERED_ROWS) {
+        // out[e, f, g]: rows f are contiguous over g -> transpose so that 8 lanes cover 128 bytes of one row
+        const uint32_t tile = pp.tiles0 + static_cast<uint32_t>(warp) * 4096u;
+        const int nblk = (bn + 31) >> 5;
+        for (int c = half; c < nblk; c += 2) {
+          const int gcol0 = g0 + c * 32;
+          warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 32), tile, lane, pp.nk > 0,
+                          [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                            const int f = f0 + lg * 32 + row;
+                            const int g = gcol0 + cj;
+                            if (f < p.FG && g < p.FD) {
+                              const long long off = (static_cast<long long>(e) * p.FG + f) * p.FD + g;
+                              if (p.splits > 1) red4(p.acc + off, x0, x1, x2, x3);
+                              else store4(out + off, x0, x1, x2, x3);
+                            }
+                          });
         }
-        const int g = g0 + c * 16;
-        const int nvalid = min(16, p.FD - g);
-        if (f < p.FG && nvalid > 0) {
-          if (p.out_layout == EGS_DW_GATHERED_ROWS) {
-            const long long off = (static_cast<long long>(e) * p.FG + f) * p.FD + g;
-            if (p.splits > 1) red_vec(p.acc + off, v, nvalid);
-            else store_vec(out + off, v, nvalid);
+      } else {
+        // out[e, g, f]: for a fixed g consecutive lanes (f) are already contiguous in memory
+        const int f = f0 + lg * 32 + lane;
+        const int nch = bn >> 4;
+        for (int c = half; c < nch; c += 2) {
+          uint32_t v[16];
+          if (pp.nk > 0) {
+            tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
+            tmem_ld_wait();
           } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0u;
+          }
+          const int g = g0 + c * 16;
+          const int nvalid = min(16, p.FD - g);
+          if (f < p.FG && nvalid > 0) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               if (i < nvalid) {
@@ -916,7 +966,8 @@ static cudaError_t ensure_smem_optin() {
 
 cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision, size_t smem_bytes,
                                   cudaStream_t st) {
-  dim3 grid((p.M + kTileM - 1) / kTileM, (p.N + p.BN - 1) / p.BN, p.E);
+  const int row_tiles = (p.M + kTileM - 1) / kTileM;
+  dim3 grid(p.expert_fastest ? p.E : row_tiles, (p.N + p.BN - 1) / p.BN, p.expert_fastest ? row_tiles : p.E);
   dim3 block(kThreads);
   cudaError_t err = cudaSuccess;
 #define EGS_LAUNCH(TY, STRICT)                                                                  \
