@@ -24,6 +24,8 @@ bool valid_index(int d) { return d == EGS_I16 || d == EGS_I32 || d == EGS_I64; }
 int elem_size(int d) { return d == EGS_F32 ? 4 : 2; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 constexpr long long kInt32Max = 2147483647LL;
+// 16-bit scatter adds directly into the output while no token row receives more contributions than this.
+constexpr int kDirect16Limit = 32;
 
 bool device_is_sm100() {
   static thread_local int cached_dev = -1;
@@ -72,15 +74,34 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   const bool no_work = (d.B * d.E * d.K == 0);
   if (!no_work && (!A || !W || !Ind) && d.C > 0) return EGS_ERR_INVALID_ARGUMENT;
 
-  // 16-bit scatter: contributions are summed in float32 scratch rows and rounded once at the end
+  // 16-bit scatter.  Workspace layout: [plan flag, 256 B][per-token counters, B*T ints][float32 rows, B*T*N].
+  // Generic kernels always sum in the float32 rows; the tensor-core path lets a planning kernel decide per call
+  // between those and direct 16-bit additions (see egs_generic.cu).
   const bool f32_rows = scatter && dtype != EGS_F32;
   const size_t n_out = static_cast<size_t>(out_rows) * d.N;
   float* acc = nullptr;
+  int* plan = nullptr;
+  const bool eligible = device_is_sm100() && rowgemm_tensor_ok(d, dtype, A, W, Out);
+  if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
+  const bool tensor = (path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible);
   if (f32_rows) {
-    if (!workspace || workspace_bytes < n_out * sizeof(float) || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
-    acc = static_cast<float*>(workspace);
-    cudaError_t err = zero_output ? launch_fill_zero(acc, n_out * sizeof(float), st)
-                                  : launch_convert_to_f32(Out, acc, n_out, dtype, st);
+    const size_t need = egs_scatter_workspace_bytes(d.B, d.T, d.N, dtype);
+    if (!workspace || workspace_bytes < need || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    const size_t counter_bytes = (static_cast<size_t>(out_rows) * sizeof(int) + 255) & ~static_cast<size_t>(255);
+    int* counters = reinterpret_cast<int*>(ws + 256);
+    acc = reinterpret_cast<float*>(ws + 256 + counter_bytes);
+    cudaError_t err;
+    if (tensor && !no_work && d.C > 0) {
+      plan = reinterpret_cast<int*>(ws);
+      err = launch_fill_zero(ws, 256 + counter_bytes, st);
+      if (err == cudaSuccess)
+        err = launch_scatter_plan(Ind, index_dtype, static_cast<int>(d.B), static_cast<int>(d.T), static_cast<int>(d.E),
+                                  static_cast<int>(d.K), counters, plan, kDirect16Limit, status, st);
+      if (err == cudaSuccess) err = launch_scatter_init(plan, acc, Out, n_out, zero_output, dtype, st);
+    } else {
+      err = zero_output ? launch_fill_zero(acc, n_out * sizeof(float), st) : launch_convert_to_f32(Out, acc, n_out, dtype, st);
+    }
     if (err != cudaSuccess) return fail_cuda(err, "scatter scratch init");
   } else if (scatter && zero_output) {
     cudaError_t err = launch_fill_zero(Out, out_bytes, st);
@@ -88,7 +109,8 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   }
   auto finish_rows = [&]() -> int {
     if (!f32_rows) return EGS_OK;
-    cudaError_t err = launch_convert_from_f32(acc, Out, n_out, dtype, st);
+    cudaError_t err = plan ? launch_scatter_finish(plan, acc, Out, n_out, dtype, st)
+                           : launch_convert_from_f32(acc, Out, n_out, dtype, st);
     return err == cudaSuccess ? EGS_OK : fail_cuda(err, "scatter scratch convert");
   };
   if (no_work) return finish_rows();
@@ -101,15 +123,12 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   }
 
   RowGemmParams p{};
-  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.acc = acc; p.status = status;
+  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.acc = acc; p.plan = plan; p.status = status;
   p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
   p.C = static_cast<int>(d.C); p.N = static_cast<int>(d.N);
   p.M = static_cast<int>(d.B * d.K);
   p.w_layout = w_layout; p.index_dtype = index_dtype;
 
-  const bool eligible = device_is_sm100() && rowgemm_tensor_ok(d, dtype, A, W, Out);
-  if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
-  const bool tensor = (path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible);
   cudaError_t err;
   if (tensor) {
     // grid order: see the kernel's comment.  Token rows touched: X rows for G, the (float32) rows added to for S.
@@ -165,7 +184,8 @@ int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, c
 
 size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype) {
   if (dtype == EGS_F32 || B <= 0 || T <= 0 || N <= 0) return 0;
-  return static_cast<size_t>(B) * T * N * sizeof(float);
+  const size_t counter_bytes = (static_cast<size_t>(B) * T * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  return 256 + counter_bytes + static_cast<size_t>(B) * T * N * sizeof(float);
 }
 
 size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype) {

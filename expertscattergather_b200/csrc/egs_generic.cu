@@ -240,6 +240,55 @@ __global__ void __launch_bounds__(256) convert_to_f32_kernel(const T* __restrict
     dst[i] = to_f32<T>(src[i]);
 }
 
+// ---- 16-bit scatter planning -------------------------------------------------------------------
+// Adding straight into a bf16/fp16 output rounds at every addition, which is accurate enough only while few
+// contributions meet in one token row; summing in float32 rows and rounding once is always accurate but costs
+// a float32 fill, float32 atomics on a buffer twice the size and a conversion pass.  The choice is made on the
+// device, per call, from the actual indices: plan != 0 selects the float32 rows.
+__global__ void __launch_bounds__(256) scatter_plan_kernel(const void* __restrict__ ind, int index_dtype, int B, int T, int E,
+                                                          int K, int* __restrict__ counters, int* __restrict__ plan,
+                                                          int limit) {
+  const long long n = static_cast<long long>(B) * E * K;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long s = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; s < n; s += stride) {
+    const long long t = load_index(ind, index_dtype, s);
+    if (t < 0 || t >= T) continue;
+    const long long b = s / (static_cast<long long>(E) * K);
+    if (atomicAdd(counters + b * T + t, 1) + 1 > limit) *plan = 1;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scatter_init_kernel(const int* __restrict__ plan, float* __restrict__ acc,
+                                                          T* __restrict__ out, size_t n, int zero_output) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (*plan) {   // float32 rows: zero them, or seed them with what the output holds
+    if (zero_output) {
+      float4* a4 = reinterpret_cast<float4*>(acc);
+      const size_t n4 = n / 4;
+      for (size_t i = i0; i < n4; i += stride) a4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (size_t i = n4 * 4 + i0; i < n; i += stride) acc[i] = 0.f;
+    } else {
+      for (size_t i = i0; i < n; i += stride) acc[i] = to_f32<T>(out[i]);
+    }
+  } else if (zero_output) {   // direct adds: only the 16-bit output needs zeroing
+    uint4* o16 = reinterpret_cast<uint4*>(out);
+    const size_t n8 = n / 8;
+    for (size_t i = i0; i < n8; i += stride) o16[i] = make_uint4(0, 0, 0, 0);
+    for (size_t i = n8 * 8 + i0; i < n; i += stride) out[i] = from_f32<T>(0.f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scatter_finish_kernel(const int* __restrict__ plan, const float* __restrict__ acc,
+                                                            T* __restrict__ out, size_t n) {
+  if (!*plan) return;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = from_f32<T>(acc[i]);
+}
+
 int grid_for(size_t work_items, int per_block) {
   size_t blocks = (work_items + per_block - 1) / per_block;
   const size_t cap = 148 * 8;   // a few waves of the 148 SMs; the kernels use grid-stride loops
@@ -296,6 +345,38 @@ cudaError_t launch_convert_from_f32(const float* src, void* dst, size_t n, int d
   if (dtype == EGS_F16) convert_from_f32_kernel<__half><<<grid, 256, 0, st>>>(src, static_cast<__half*>(dst), n);
   else if (dtype == EGS_BF16)
     convert_from_f32_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  else return cudaErrorInvalidValue;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_plan(const void* Ind, int index_dtype, int B, int T, int E, int K, int* counters, int* plan,
+                                int limit, int32_t*, cudaStream_t st) {
+  const size_t n = static_cast<size_t>(B) * E * K;
+  if (n == 0) return cudaSuccess;
+  scatter_plan_kernel<<<grid_for(n, 256), 256, 0, st>>>(Ind, index_dtype, B, T, E, K, counters, plan, limit);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_init(const int* plan, float* acc, void* out16, size_t n, int zero_output, int dtype,
+                                cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  const int grid = grid_for(n, 256 * 8);
+  if (dtype == EGS_F16) scatter_init_kernel<__half><<<grid, 256, 0, st>>>(plan, acc, static_cast<__half*>(out16), n, zero_output);
+  else if (dtype == EGS_BF16)
+    scatter_init_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(plan, acc, static_cast<__nv_bfloat16*>(out16), n, zero_output);
+  else return cudaErrorInvalidValue;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_finish(const int* plan, const float* acc, void* out16, size_t n, int dtype, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  const int grid = grid_for(n, 256 * 4);
+  if (dtype == EGS_F16) scatter_finish_kernel<__half><<<grid, 256, 0, st>>>(plan, acc, static_cast<__half*>(out16), n);
+  else if (dtype == EGS_BF16)
+    scatter_finish_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(plan, acc, static_cast<__nv_bfloat16*>(out16), n);
   else return cudaErrorInvalidValue;
   count_launch();
   return cudaGetLastError();

@@ -45,6 +45,8 @@ struct RowGemmParams {
   const void* Ind;    // [B, E, K]
   void* Out;          // G: slot rows [B*E*K, N]     S: token rows [B*T, N]
   float* acc;         // S with 16-bit tensors: float32 accumulation rows [B*T, N]; otherwise unused
+  const int* plan;    // S with 16-bit tensors: device flag, non-zero = accumulate in the float32 rows,
+                      // zero = add directly into the 16-bit output; NULL = always the float32 rows
   int32_t* status;    // optional device status word
   int B, T, E, K, C, N;
   int M;              // expert rows per expert = B*K
@@ -80,6 +82,13 @@ cudaError_t launch_generic_dweight(const DWeightParams& p, int dtype, cudaStream
 cudaError_t launch_fill_zero(void* ptr, size_t bytes, cudaStream_t st);
 cudaError_t launch_convert_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t st);
 cudaError_t launch_convert_to_f32(const void* src, float* dst, size_t n, int dtype, cudaStream_t st);
+// 16-bit scatter planning (see egs_generic.cu): counts contributions per token row and raises *plan when any
+// row receives more than `limit`; the init / finish kernels then act on the float32 rows or on the 16-bit output.
+cudaError_t launch_scatter_plan(const void* Ind, int index_dtype, int B, int T, int E, int K, int* counters, int* plan,
+                                int limit, int32_t* status, cudaStream_t st);
+cudaError_t launch_scatter_init(const int* plan, float* acc, void* out16, size_t n, int zero_output, int dtype,
+                                cudaStream_t st);
+cudaError_t launch_scatter_finish(const int* plan, const float* acc, void* out16, size_t n, int dtype, cudaStream_t st);
 
 // Tensor-core (tcgen05) family.  `configure_*` fills BN/stages and returns the dynamic shared memory size.
 size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision);

@@ -286,6 +286,12 @@ __device__ __forceinline__ void red4(float* dst, uint32_t x0, uint32_t x1, uint3
                "f"(__uint_as_float(x2)), "f"(__uint_as_float(x3))
                : "memory");
 }
+__device__ __forceinline__ void red4(__nv_bfloat16* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+  asm volatile("red.global.add.noftz.v2.bf16x2 [%0], {%1,%2};" ::"l"(dst), "r"(pack2(dst, x0, x1)), "r"(pack2(dst, x2, x3)) : "memory");
+}
+__device__ __forceinline__ void red4(__half* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+  asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1,%2};" ::"l"(dst), "r"(pack2(dst, x0, x1)), "r"(pack2(dst, x2, x3)) : "memory");
+}
 __device__ __forceinline__ void store4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
   *reinterpret_cast<uint4*>(dst) = make_uint4(x0, x1, x2, x3);
 }
@@ -597,6 +603,8 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
       const uint32_t tile = pp.tiles0 + static_cast<uint32_t>(warp) * 4096u;
       T* out = static_cast<T*>(p.Out);
       float* acc_rows = (ES == 2) ? p.acc : reinterpret_cast<float*>(p.Out);   // S: float32 rows being added to
+      // 16-bit S: the planning flag says whether to add into the float32 rows or straight into the output
+      const bool direct16 = SCATTER && ES == 2 && p.plan != nullptr && *p.plan == 0;
       const int nblk = (bn + 31) >> 5;
       for (int c = half; c < nblk; c += 2) {
         const int col0 = n0 + c * 32;
@@ -606,8 +614,12 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
                           const int col = col0 + cj;
                           if (ro >= 0 && col < p.N) {
                             const long long off = static_cast<long long>(ro) * p.N + col;
-                            if (SCATTER) red4(acc_rows + off, x0, x1, x2, x3);
-                            else store4(out + off, x0, x1, x2, x3);   // masked source rows were zero-filled: zeros
+                            if (SCATTER) {
+                              if (direct16) red4(out + off, x0, x1, x2, x3);
+                              else red4(acc_rows + off, x0, x1, x2, x3);
+                            } else {
+                              store4(out + off, x0, x1, x2, x3);   // masked source rows were zero-filled: zeros
+                            }
                           }
                         });
       }

@@ -89,15 +89,16 @@ int egs_gather_gemm(const void* X, const void* W, const void* Ind, void* Y, cons
  * zero_output != 0: Out is zero-filled first on the same stream (the reference's forward forgets to,
  * egs/triton_kernels.py:457); zero_output == 0: contributions are added to what Out holds.
  * Duplicate token ids accumulate.  The additions are atomic and their order is not fixed.
- * 16-bit tensors are accumulated in float32 and rounded once: workspace must then hold
- * egs_scatter_workspace_bytes() bytes of device scratch (contents on entry do not matter); for float32
- * tensors it may be NULL.
+ * 16-bit tensors need egs_scatter_workspace_bytes() bytes of device scratch in workspace (contents on
+ * entry do not matter; NULL is fine for float32 tensors): a planning kernel counts the contributions per
+ * token row; while no row receives more than 32 the products are added straight into the 16-bit output,
+ * otherwise they are summed in float32 rows of the scratch and rounded once at the end.
  */
 int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, const egs_dims* dims,
                      int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path,
                      void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
 
-/* Scratch bytes egs_gemm_scatter needs (0 for float32 tensors, B*T*N*4 for 16-bit ones).  No reference
+/* Scratch bytes egs_gemm_scatter needs (0 for float32 tensors; counters + B*T*N*4 for 16-bit ones).  No reference
  * counterpart: the reference adds atomically in the output dtype (egs/triton_kernels.py:247). */
 size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype);
 

@@ -69,4 +69,4 @@ def test_workspace_size_rule():
     assert lib.egs_dw_workspace_bytes(4, 8, 16, _lib.BF16) == 4 * 8 * 16 * 4
     assert lib.egs_dw_workspace_bytes(0, 8, 16, _lib.BF16) == 0
     assert lib.egs_scatter_workspace_bytes(2, 8, 16, _lib.F32) == 0
-    assert lib.egs_scatter_workspace_bytes(2, 8, 16, _lib.F16) == 2 * 8 * 16 * 4
+    assert lib.egs_scatter_workspace_bytes(2, 8, 16, _lib.F16) == 256 + 256 + 2 * 8 * 16 * 4
