@@ -70,6 +70,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 // Hardware arrive on an mbarrier once all cp.async copies this thread has issued so far have landed.
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -585,10 +588,40 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
         }
       }
     };
+    // Lean issue path for interior stages of full tiles (every row valid, the stage inside the contraction
+    // range): no predicates, destination offsets are immediates, about two instructions per copy.
+    const bool a_full = (a_mask == (1u << (kTileM / 32)) - 1u);
+    const bool nc_full = w_nc && (p.BN % 32 == 0) && (n0 + p.BN <= p.N);
+    const bool cn_full = !w_nc && cn_fast && (KE % cn_rstep == 0) && (cn_rstep % 8 == 0 || kMn32) &&
+                         (static_cast<long long>(n0) * ES + cpr * 16 <= row_bytes_w);
+    const bool tile_full = a_full && (nc_full || cn_full);
+    const uint32_t cn_dst0 = cn_dst_seg + static_cast<uint32_t>(cn_r0) * 128u +
+                             (kMn32 ? ((static_cast<uint32_t>(((cn_c & 7) >> 1) ^ (cn_r0 & 3)) << 5) + (static_cast<uint32_t>(cn_c & 1) << 4))
+                                    : (static_cast<uint32_t>((cn_c & 7) ^ (cn_r0 & 7)) << 4));
+    auto issue_full = [&](int kt, uint32_t stage_base) {
+      const long long koff = static_cast<long long>(kt) * 128;
+      const uint32_t da = stage_base + rc_dst0;
+#pragma unroll
+      for (int i = 0; i < kTileM / 32; ++i) cp_async16_full(da + i * 4096u, a_src[i] + koff);
+      if (w_nc) {
+        const char* src = nc_src0 + koff;
+        const uint32_t db = da + b_off;
+        for (int i = 0; i < nb_iters; ++i, src += nc_stride) cp_async16_full(db + i * 4096u, src);
+      } else {
+        const char* src = cn_src0 + static_cast<long long>(kt * KE) * row_bytes_w;
+        const uint32_t db = stage_base + b_off + cn_dst0;
+        const uint32_t dstep = static_cast<uint32_t>(cn_rstep) * 128u;
+        for (int r = cn_r0, i = 0; r < KE; r += cn_rstep, ++i, src += cn_stride) cp_async16_full(db + i * dstep, src);
+      }
+    };
     const bool alive = run_producer<STRICT>(
         pp, lane,
         [&](int kt, uint32_t base) {
-          for_each_chunk(kt, base, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : W, v ? 16u : 0u); });
+          if (tile_full && (kt + 1) * KE <= p.C) {
+            issue_full(kt, base);
+          } else {
+            for_each_chunk(kt, base, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : W, v ? 16u : 0u); });
+          }
         },
         [&](int kc, uint32_t base) {
           for_each_chunk(kc, base, [&](uint32_t dst, const char*, bool, bool is_b) {
@@ -786,10 +819,52 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
         }
       }
     };
+    // Lean issue path for interior stages of full tiles (all KR rows inside this CTA's range with valid token
+    // ids is not known statically, so rows keep their validity test; columns and the B walk are unpredicated).
+    const bool a_cols_full = static_cast<long long>(f0) * ES + CPR_A * 16 <= row_bytes_g;
+    const bool b_cols_full = b_fast && (KR % b_rstep == 0) && (b_rstep % 8 == 0 || kMn32) &&
+                             (static_cast<long long>(g0) * ES + cpr_b * 16 <= row_bytes_d);
+    const bool tile_full = a_cols_full && b_cols_full;
+    const uint32_t a_dst0 = a_dst_seg + static_cast<uint32_t>(a_r0) * 128u + swz(a_c, a_r0);
+    const uint32_t b_dst0 = b_dst_seg + static_cast<uint32_t>(b_r0) * 128u + swz(b_c, b_r0);
+    const unsigned row_bytes_g32 = static_cast<unsigned>(row_bytes_g);
+    // B source pointer of this thread's first row, carried across stages: rows ascend by b_rstep, a wrap of k
+    // into the next batch element jumps (E-1)*K slot rows
+    int bk = (m_begin + b_r0) % p.K;
+    const char* b_ptr = b_col + (static_cast<long long>((m_begin + b_r0) / p.K * p.E + e) * p.K + bk) * row_bytes_d;
+    const long long b_row_step = static_cast<long long>(b_rstep) * row_bytes_d;
+    const long long b_wrap_step = static_cast<long long>(p.E - 1) * p.K * row_bytes_d;
+    int b_next_kt = 0;     // the stage b_ptr currently points into
+    auto issue_full = [&](int kt, uint32_t stage_base) {
+      const int i0 = kt * KR;
+      const uint32_t da = stage_base + a_dst0;
+#pragma unroll
+      for (int i = 0; i < KR / a_rstep; ++i) {
+        const int tok = row_tok[i0 + a_r0 + i * a_rstep];
+        const bool v = tok >= 0;
+        cp_async16(da + i * (a_rstep * 128u), a_col + static_cast<unsigned long long>(static_cast<unsigned>(v ? tok : 0)) * row_bytes_g32,
+                   v ? 16u : 0u);
+      }
+      const uint32_t db = stage_base + b_off + b_dst0;
+      const uint32_t dstep = static_cast<uint32_t>(b_rstep) * 128u;
+      const int iters = KR / b_rstep;
+      for (int i = 0; i < iters; ++i) {
+        cp_async16_full(db + i * dstep, b_ptr);
+        b_ptr += b_row_step;
+        bk += b_rstep;
+        while (bk >= p.K) { bk -= p.K; b_ptr += b_wrap_step; }
+      }
+      b_next_kt = kt + 1;
+    };
     const bool alive = run_producer<STRICT>(
         pp, lane,
         [&](int kt, uint32_t base) {
-          for_each_chunk(kt, base, true, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : Xs, v ? 16u : 0u); });
+          // the lean path walks b_ptr stage by stage, so it serves a prefix of consecutive full stages
+          if (tile_full && kt == b_next_kt && (kt + 1) * KR <= rows) {
+            issue_full(kt, base);
+          } else {
+            for_each_chunk(kt, base, true, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : Xs, v ? 16u : 0u); });
+          }
         },
         [&](int kc, uint32_t base) {
           for_each_chunk(kc, base, false, [&](uint32_t dst, const char*, bool, bool is_b) {
