@@ -135,7 +135,7 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     const double act_bytes = static_cast<double>(d.B) * d.T * (scatter ? d.N * 4.0 : d.C * static_cast<double>(elem_size(dtype)));
     const double w_bytes = static_cast<double>(d.E) * d.C * d.N * elem_size(dtype);
     p.expert_fastest = (act_bytes > 96e6 && w_bytes < 64e6 && (d.B * d.K + 127) / 128 <= 65535) ? 1 : 0;
-    const size_t smem = configure_tensor_rowgemm(p, dtype, precision);
+    const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
     err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
   } else {
     err = launch_generic_rowgemm(p, scatter, dtype, st);

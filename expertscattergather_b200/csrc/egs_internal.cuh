@@ -55,6 +55,7 @@ struct RowGemmParams {
   int BN;             // tensor path: tile width over N (multiple of 16, <= 256)
   int stages;         // tensor path: pipeline depth
   int expert_fastest; // tensor path: grid order (1: experts vary fastest, row tiles slowest)
+  int row_tiles;      // tensor path: 128-row accumulator tiles per CTA (1 or 2)
 };
 
 struct DWeightParams {
@@ -91,7 +92,7 @@ cudaError_t launch_scatter_init(const int* plan, float* acc, void* out16, size_t
 cudaError_t launch_scatter_finish(const int* plan, const float* acc, void* out16, size_t n, int dtype, cudaStream_t st);
 
 // Tensor-core (tcgen05) family.  `configure_*` fills BN/stages and returns the dynamic shared memory size.
-size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision);
+size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int precision);
 size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision);
 cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision,
                                   size_t smem_bytes, cudaStream_t st);

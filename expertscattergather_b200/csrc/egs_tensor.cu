@@ -45,7 +45,7 @@ constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kThreads = kProducerThreads + 32;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kHeaderBytes = 2048;
+constexpr uint32_t kHeaderBytes = 3072;
 constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 clocks
 
 constexpr int kMaxRowsPerSplit = 4096;   // operator D: contraction rows one CTA may own (row table in smem)
@@ -56,8 +56,8 @@ struct __align__(16) SmemHeader {
   unsigned long long done;
   uint32_t tmem_base;
   uint32_t abort_flag;
-  int row_a[kTileM];   // rowgemm: source row index per tile row (-1 = masked)
-  int row_o[kTileM];   // rowgemm: destination row index per tile row (-1 = masked)
+  int row_a[2 * kTileM];   // rowgemm: source row index per CTA row (-1 = masked)
+  int row_o[2 * kTileM];   // rowgemm: destination row index per CTA row (-1 = masked)
 };
 static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header does not fit");
 
@@ -316,7 +316,7 @@ __device__ __forceinline__ char* aligned_smem(unsigned char* raw) {
 
 // Optional phase trace (compile with -DEGS_TRACE): CTA (0,0,0) records globaltimer stamps of its phases.
 #ifdef EGS_TRACE
-__device__ unsigned long long g_trace[32];
+__device__ unsigned long long g_trace[256];
 __device__ __forceinline__ void trace_mark(int slot) {
   if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
     unsigned long long t;
@@ -391,8 +391,10 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
       const int slot = kt % stages, use = kt / stages;
       if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
       if (!alive) break;
+      if (threadIdx.x == 0 && kt < 64) EGS_MARK(32 + kt);
       issue(kt, pp.tiles0 + slot * pp.stage_bytes);
       cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
+      if (threadIdx.x == 0 && kt < 64) EGS_MARK(96 + kt);
     }
   } else {
     const int dist = stages - 1;
@@ -441,6 +443,7 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
     if (!ok) break;
     tc_fence_after();
     if (ks == 0) EGS_MARK(6);
+    if (ks < 64) EGS_MARK(160 + ks);
     mma(ks, pp.tiles0 + slot * pp.stage_bytes);
     umma_commit(smem_u32(&hdr->empty[slot]));
   }
@@ -457,8 +460,12 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
 //   B = W[e]:  EGS_W_NC -> rows n, contraction contiguous (K-major);  EGS_W_CN -> rows c, n contiguous (MN-major)
 //   epilogue:  G stores slot rows;  S adds to token rows with vector red.global.add.f32
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool STRICT, bool SCATTER>
-__global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kernel(RowGemmParams p) {
+// MT = number of 128-row accumulator tiles per CTA (1 or 2).  With MT = 2 the CTA owns 256 expert rows: both
+// accumulators are fed from the same W tile, which cuts the bytes loaded per flop by a third and lets a
+// three-stage ring of one CTA per SM cover the load latency that two 2-stage CTAs cannot.
+template <typename T, bool STRICT, bool SCATTER, int MT>
+__global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_rowgemm_kernel(RowGemmParams p) {
+  constexpr int kRows = kTileM * MT;        // expert rows per CTA
   constexpr int ES = sizeof(T);
   constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
   constexpr int UK = 32 / ES;         // contraction elements per tcgen05.mma
@@ -472,12 +479,12 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) EGS_MARK(0);
   const int e = p.expert_fastest ? blockIdx.x : blockIdx.z;
-  const int m0 = (p.expert_fastest ? blockIdx.z : blockIdx.x) * kTileM;
+  const int m0 = (p.expert_fastest ? blockIdx.z : blockIdx.x) * kRows;
   const int n0 = blockIdx.y * p.BN;
   const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);       // MMA N of this tile (multiple of 16)
   const bool w_nc = (p.w_layout == EGS_W_NC);
 
-  const uint32_t a_bytes = kTileM * 128u;
+  const uint32_t a_bytes = kRows * 128u;
   const int nseg_b = (p.BN * ES + 127) / 128;
   const uint32_t b_bytes = w_nc ? static_cast<uint32_t>(p.BN) * 128u : static_cast<uint32_t>(nseg_b) * KE * 128u;
   const uint32_t a_lo_off = a_bytes;                                   // strict: A_hi | A_lo | B_hi | B_lo
@@ -494,7 +501,7 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
   pp.nk = (p.C + KE - 1) / KE;
 
   // ---- set-up ----
-  if (tid < kTileM) {
+  if (tid < kRows) {
     const int m = m0 + tid;
     int ra = -1, ro = -1;
     if (m < p.M) {
@@ -513,7 +520,8 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
     hdr->row_a[tid] = ra;
     hdr->row_o[tid] = ro;
   }
-  const uint32_t tmem_cols = tmem_cols_for(p.BN);
+  const uint32_t acc_cols = tmem_cols_for(p.BN);      // columns of one accumulator
+  const uint32_t tmem_cols = acc_cols * MT;
   const uint32_t tmem_base = pipe_setup(pp, STRICT ? kProducerWarps : kProducerThreads, tmem_cols, tid, warp);
   const bool run = (hdr->abort_flag == 0u);
 
@@ -533,10 +541,10 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
     const int cc = tid & 7;
     const int r0 = tid >> 3;
     const uint32_t rc_dst0 = static_cast<uint32_t>(r0) * 128u + (static_cast<uint32_t>(cc ^ (r0 & 7)) << 4);
-    const char* a_src[kTileM / 32];
+    const char* a_src[kRows / 32];
     uint32_t a_mask = 0;
 #pragma unroll
-    for (int i = 0; i < kTileM / 32; ++i) {
+    for (int i = 0; i < kRows / 32; ++i) {
       const int ra = hdr->row_a[r0 + 32 * i];
       a_src[i] = A + (ra >= 0 ? static_cast<long long>(ra) * row_bytes_a : 0ll) + cc * 16;
       if (ra >= 0) a_mask |= 1u << i;
@@ -564,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
       const long long koff = static_cast<long long>(k0) * ES;
       const bool kvalid = koff + cc * 16 < row_bytes_a;
 #pragma unroll
-      for (int i = 0; i < kTileM / 32; ++i)
+      for (int i = 0; i < kRows / 32; ++i)
         f(stage_base + rc_dst0 + i * 4096u, a_src[i] + koff, kvalid && ((a_mask >> i) & 1u), false);
       if (w_nc) {
         const char* src = nc_src0 + koff;
@@ -590,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
     };
     // Lean issue path for interior stages of full tiles (every row valid, the stage inside the contraction
     // range): no predicates, destination offsets are immediates, about two instructions per copy.
-    const bool a_full = (a_mask == (1u << (kTileM / 32)) - 1u);
+    const bool a_full = (a_mask == (1u << (kRows / 32)) - 1u);
     const bool nc_full = w_nc && (p.BN % 32 == 0) && (n0 + p.BN <= p.N);
     const bool cn_full = !w_nc && cn_fast && (KE % cn_rstep == 0) && (cn_rstep % 8 == 0 || kMn32) &&
                          (static_cast<long long>(n0) * ES + cpr * 16 <= row_bytes_w);
@@ -602,7 +610,7 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
       const long long koff = static_cast<long long>(kt) * 128;
       const uint32_t da = stage_base + rc_dst0;
 #pragma unroll
-      for (int i = 0; i < kTileM / 32; ++i) cp_async16_full(da + i * 4096u, a_src[i] + koff);
+      for (int i = 0; i < kRows / 32; ++i) cp_async16_full(da + i * 4096u, a_src[i] + koff);
       if (w_nc) {
         const char* src = nc_src0 + koff;
         const uint32_t db = da + b_off;
@@ -639,22 +647,24 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
       // 16-bit S: the planning flag says whether to add into the float32 rows or straight into the output
       const bool direct16 = SCATTER && ES == 2 && p.plan != nullptr && *p.plan == 0;
       const int nblk = (bn + 31) >> 5;
-      for (int c = half; c < nblk; c += 2) {
-        const int col0 = n0 + c * 32;
-        warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 32), tile, lane, true,
-                        [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-                          const int ro = hdr->row_o[lg * 32 + row];
-                          const int col = col0 + cj;
-                          if (ro >= 0 && col < p.N) {
-                            const long long off = static_cast<long long>(ro) * p.N + col;
-                            if (SCATTER) {
-                              if (direct16) red4(out + off, x0, x1, x2, x3);
-                              else red4(acc_rows + off, x0, x1, x2, x3);
-                            } else {
-                              store4(out + off, x0, x1, x2, x3);   // masked source rows were zero-filled: zeros
+      for (int mt = 0; mt < MT; ++mt) {
+        for (int c = half; c < nblk; c += 2) {
+          const int col0 = n0 + c * 32;
+          warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + mt * acc_cols + static_cast<uint32_t>(c * 32), tile,
+                          lane, true, [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                            const int ro = hdr->row_o[mt * kTileM + lg * 32 + row];
+                            const int col = col0 + cj;
+                            if (ro >= 0 && col < p.N) {
+                              const long long off = static_cast<long long>(ro) * p.N + col;
+                              if (SCATTER) {
+                                if (direct16) red4(out + off, x0, x1, x2, x3);
+                                else red4(acc_rows + off, x0, x1, x2, x3);
+                              } else {
+                                store4(out + off, x0, x1, x2, x3);   // masked source rows were zero-filled: zeros
+                              }
                             }
-                          }
-                        });
+                          });
+        }
       }
     }
   } else {
@@ -671,16 +681,21 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_rowgemm_kerne
         const int nkq = min(KE / UK, (krem + UK - 1) / UK);
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
-          const uint64_t ad = make_smem_desc(a_hi + kq * 32u, 16u, 1024u);
           const uint64_t bd = make_smem_desc(b_hi + kq * b_step, b_lbo, b_sbo, b_lay);
-          if (STRICT) {
-            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + kq * 32u, 16u, 1024u);
-            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + kq * b_step, b_lbo, b_sbo, b_lay);
-            umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
-            umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
-            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
-          } else {
-            umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
+          const uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off + kq * b_step, b_lbo, b_sbo, b_lay) : 0ull;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t d = tmem_base + mt * acc_cols;
+            const uint32_t a_mt = a_hi + mt * (kTileM * 128u) + kq * 32u;
+            const uint64_t ad = make_smem_desc(a_mt, 16u, 1024u);
+            if (STRICT) {
+              const uint64_t adl = make_smem_desc(a_mt + a_lo_off, 16u, 1024u);
+              umma<Elem<T>::tf32>(d, adl, bd, idesc, acc);
+              umma<Elem<T>::tf32>(d, ad, bdl, idesc, 1u);
+              umma<Elem<T>::tf32>(d, ad, bd, idesc, 1u);
+            } else {
+              umma<Elem<T>::tf32>(d, ad, bd, idesc, acc);
+            }
           }
         }
       });
@@ -974,9 +989,10 @@ int tile_n_cap(int dflt) {
 // loop of the other); grids that fit in one wave take the whole SM.
 int pick_stages(size_t fixed_bytes, size_t stage_bytes, long long ctas, bool allow_two_per_sm) {
   static const int env = env_int("EGS_B200_STAGES");
+  static const int one_cta = env_int("EGS_B200_ONE_CTA");
   const size_t two = kSmemPerSm / 2 - kSmemReservedPerCta;
   int s = 0;
-  if (allow_two_per_sm && ctas > kSmCount && fixed_bytes + 2 * stage_bytes <= two)
+  if (allow_two_per_sm && !one_cta && ctas > kSmCount && fixed_bytes + 2 * stage_bytes <= two)
     s = static_cast<int>((two - fixed_bytes) / stage_bytes);
   else
     s = static_cast<int>((kSmemMaxPerCta - fixed_bytes) / stage_bytes);
@@ -987,7 +1003,7 @@ int pick_stages(size_t fixed_bytes, size_t stage_bytes, long long ctas, bool all
 
 }  // namespace
 
-size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision) {
+size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int precision) {
   const int es = (dtype == EGS_F32) ? 4 : 2;
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int ke = 128 / es;
@@ -995,13 +1011,21 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, int dtype, int precision) {
   const int cap = tile_n_cap(strict ? 128 : 256);
   if (bn > cap) bn = cap;
   p.BN = bn;
-  const size_t a_bytes = kTileM * 128;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t b_bytes = (p.w_layout == EGS_W_NC) ? static_cast<size_t>(bn) * 128 : nseg_b * ke * 128;
-  const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
   const size_t fixed = 1024 + kHeaderBytes;
-  const long long ctas = static_cast<long long>((p.M + kTileM - 1) / kTileM) * ((p.N + bn - 1) / bn) * p.E;
-  p.stages = pick_stages(fixed, stage_bytes, ctas, !strict);
+  const long long n_tiles = (p.N + bn - 1) / bn;
+  // 256-row CTAs (two accumulators): when the grid still fills the SMs at least once, the contraction is long
+  // enough for the deeper ring to matter, and the two accumulators fit in tensor memory
+  static const int mt_env = env_int("EGS_B200_ROW_TILES");
+  const long long ctas2 = static_cast<long long>((p.M + 2 * kTileM - 1) / (2 * kTileM)) * n_tiles * p.E;
+  // (the scatter epilogue dominates short contractions and profits from two CTAs per SM instead)
+  const bool want2 = !strict && p.M >= 2 * kTileM && ctas2 >= kSmCount && p.C * es >= (scatter ? 4096 : 1024);
+  p.row_tiles = (mt_env == 1) ? 1 : (mt_env == 2 && !strict && p.M > kTileM) ? 2 : (want2 ? 2 : 1);
+  const size_t a_bytes = static_cast<size_t>(kTileM) * p.row_tiles * 128;
+  const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
+  const long long ctas = static_cast<long long>((p.M + kTileM * p.row_tiles - 1) / (kTileM * p.row_tiles)) * n_tiles * p.E;
+  p.stages = pick_stages(fixed, stage_bytes, ctas, !strict && p.row_tiles == 1);
   return fixed + p.stages * stage_bytes;
 }
 
@@ -1053,19 +1077,25 @@ static cudaError_t ensure_smem_optin() {
 
 cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision, size_t smem_bytes,
                                   cudaStream_t st) {
-  const int row_tiles = (p.M + kTileM - 1) / kTileM;
+  const int rows_per_cta = kTileM * p.row_tiles;
+  const int row_tiles = (p.M + rows_per_cta - 1) / rows_per_cta;
   dim3 grid(p.expert_fastest ? p.E : row_tiles, (p.N + p.BN - 1) / p.BN, p.expert_fastest ? row_tiles : p.E);
   dim3 block(kThreads);
   cudaError_t err = cudaSuccess;
-#define EGS_LAUNCH(TY, STRICT)                                                                  \
-  do {                                                                                          \
-    if (scatter) {                                                                              \
-      err = (ensure_smem_optin<tensor_rowgemm_kernel<TY, STRICT, true>>());                        \
-      if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, true><<<grid, block, smem_bytes, st>>>(p);  \
-    } else {                                                                                    \
-      err = (ensure_smem_optin<tensor_rowgemm_kernel<TY, STRICT, false>>());                        \
-      if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, false><<<grid, block, smem_bytes, st>>>(p); \
-    }                                                                                           \
+#define EGS_LAUNCH2(TY, STRICT, SC, MTV)                                                              \
+  do {                                                                                                \
+    err = (ensure_smem_optin<tensor_rowgemm_kernel<TY, STRICT, SC, MTV>>());                          \
+    if (err == cudaSuccess) tensor_rowgemm_kernel<TY, STRICT, SC, MTV><<<grid, block, smem_bytes, st>>>(p); \
+  } while (0)
+#define EGS_LAUNCH(TY, STRICT)                                        \
+  do {                                                                \
+    if (scatter) {                                                    \
+      if (p.row_tiles == 2 && !STRICT) EGS_LAUNCH2(TY, false, true, 2);  \
+      else EGS_LAUNCH2(TY, STRICT, true, 1);                          \
+    } else {                                                          \
+      if (p.row_tiles == 2 && !STRICT) EGS_LAUNCH2(TY, false, false, 2); \
+      else EGS_LAUNCH2(TY, STRICT, false, 1);                         \
+    }                                                                 \
   } while (0)
   if (dtype == EGS_F32) {
     if (precision == EGS_PREC_STRICT) EGS_LAUNCH(float, true);
@@ -1076,6 +1106,7 @@ cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtyp
     EGS_LAUNCH(__nv_bfloat16, false);
   }
 #undef EGS_LAUNCH
+#undef EGS_LAUNCH2
   if (err != cudaSuccess) return err;
   count_launch();
   return cudaGetLastError();
@@ -1108,7 +1139,7 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
 
 #ifdef EGS_TRACE
 extern "C" int egs_debug_trace(unsigned long long* host_out, int n) {
-  if (n > 32) n = 32;
+  if (n > 256) n = 256;
   return static_cast<int>(cudaMemcpyFromSymbol(host_out, egs::g_trace, n * sizeof(unsigned long long)));
 }
 #endif
