@@ -263,6 +263,44 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, 
   return EGS_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Weight gradient without any allocation by anybody: the float32 scratch of egs_dweight lives in a
+// file-scope device array.  In host code the array's name is only a stand-in for the symbol, not a device
+// address, so the address is asked for once per device (with that device current) and cached.
+// ------------------------------------------------------------------------------------------------
+#define EGS_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)          /* 16 MiB, held by every device that loads the library */
+static __device__ __align__(256) float g_static_dw_scratch[EGS_STATIC_SCRATCH_FLOATS];
+static float* g_static_dw_scratch_addr[64] = {};             /* per device ordinal, filled on first use */
+
+int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T,
+                               int64_t E, int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype,
+                               int precision, int path, int32_t* status_word, void* cuda_stream) {
+  // size check first: it needs no device
+  if (E < 0 || FG < 0 || FD < 0) return EGS_ERR_INVALID_ARGUMENT;
+  if (static_cast<double>(E) * static_cast<double>(FG) * static_cast<double>(FD) > static_cast<double>(EGS_STATIC_SCRATCH_FLOATS)) {
+    std::snprintf(g_cuda_error, sizeof(g_cuda_error),
+                  "egs_dweight_static_scratch: E*FG*FD = %lld elements exceed the built-in scratch of %d",
+                  static_cast<long long>(E * FG * FD), EGS_STATIC_SCRATCH_FLOATS);
+    return EGS_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return EGS_ERR_TOO_LARGE;
+  if (g_static_dw_scratch_addr[dev] == nullptr) {            // set-up: first call on this device
+    float* addr = nullptr;
+    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_dw_scratch);
+    if (err != cudaSuccess || addr == nullptr) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
+    g_static_dw_scratch_addr[dev] = addr;
+  }
+  // egs_dweight clears the part of the scratch it accumulates into before use and reads back only what it wrote
+  return egs_dweight(Xsrc, Ysrc, Ind, out, B, T, E, K, FG, FD, out_layout, dtype, index_dtype, precision, path,
+                     g_static_dw_scratch_addr[dev], sizeof(float) * static_cast<size_t>(EGS_STATIC_SCRATCH_FLOATS),
+                     status_word, cuda_stream);
+}
+
+size_t egs_static_scratch_max_elements(void) { return EGS_STATIC_SCRATCH_FLOATS; }
+
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers, int n_pointers) {
   if (!dims || !valid_dtype(dtype) || op < 0 || op > 2) return 0;
   if (!device_is_sm100()) return 0;

@@ -119,6 +119,30 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out,
  * the reference accumulates dW with atomics directly in the output dtype (egs/triton_kernels.py:356). */
 size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype);
 
+/*
+ * egs_dweight for callers that cannot hand over freshly allocated scratch.  (It has no counterpart in the
+ * reference: there every buffer comes from torch's allocator.)  Who needs it: a host that embeds this library
+ * somewhere device allocation is off limits at call time - an inference or training runtime that gives its
+ * whole memory budget to its own arena at start-up and forbids cudaMalloc afterwards, a plug-in that only ever
+ * sees the pointers of its inputs and outputs, or a latency-critical loop where an allocation could
+ * synchronise the device or fail on a fragmented heap.  Same operator and arguments as egs_dweight, minus the
+ * workspace: the float32 scratch is a 16 MiB array built into the library image (every GPU that loads the
+ * library carries it until the process exits).  The entry point itself allocates nothing and frees nothing.
+ *   - Limit: E*FG*FD <= egs_static_scratch_max_elements() (4 Mi elements); larger problems return
+ *     EGS_ERR_TOO_LARGE with an explanatory egs_last_cuda_error() text and launch nothing.
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls share the one array, and it keeps whatever the previous call left.  Each call clears what
+ *     it accumulates into, so stale contents are harmless, but two calls whose kernels may overlap on the
+ *     GPU (different streams, no ordering between them) race on it: order them.
+ */
+int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* Ind, void* out,
+                               int64_t B, int64_t T, int64_t E, int64_t K, int64_t FG, int64_t FD,
+                               int out_layout, int dtype, int index_dtype, int precision, int path,
+                               int32_t* status_word, void* cuda_stream);
+/* Capacity of the built-in scratch in float32 elements.  No counterpart in the reference. */
+size_t egs_static_scratch_max_elements(void);
+
 /* 1 if EGS_PATH_AUTO would take the tcgen05 tensor-core kernels for this operator and shape, else 0.
  * op: 0 = G, 1 = S, 2 = D (for D pass C=FG, N=FD).  No reference counterpart (diagnostic). */
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers,
