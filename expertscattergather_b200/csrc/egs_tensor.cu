@@ -228,7 +228,7 @@ __device__ __forceinline__ void split_chunk(uint32_t addr, uint32_t lo_offset) {
   for (int i = 0; i < 4; ++i) {
     const uint32_t hi = v[i] & 0xFFFFE000u;
     const float rem = __uint_as_float(v[i]) - __uint_as_float(hi);
-    asm volatile("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo[i]) : "f"(rem));
+    lo[i] = (__float_as_uint(rem) + 0x1000u) & 0xFFFFE000u;   // round to tf32 (nearest, ties away) with integer ops
     v[i] = hi;
   }
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
@@ -379,6 +379,17 @@ __device__ __forceinline__ void pipe_teardown(uint32_t tmem_base, uint32_t tmem_
   }
 }
 
+// Common end of every producer variant: drain own copies, then wait (warp-uniformly) for the accumulator.
+__device__ __forceinline__ bool producer_finish(const Pipe& pp, int lane, bool alive) {
+  cp_async_wait_all();
+  // all lanes of a warp must take the tcgen05.ld of the epilogue together: the decision is warp-uniform
+  alive = __all_sync(0xffffffffu, alive);
+  if (alive && pp.nk > 0) alive = mbar_wait_warp(smem_u32(&pp.hdr->done), 0u, pp.abort_flag, pp.status, lane);
+  if (alive) tc_fence_after();
+  if (threadIdx.x == 0) EGS_MARK(8);
+  return alive;
+}
+
 // Producer main loop.  issue(kt, stage_base) enqueues this thread's cp.async copies of stage kt;
 // split(kt, stage_base) is the strict-mode in-place hi/lo pass over the same chunks.
 template <bool STRICT, class Issue, class Split>
@@ -406,9 +417,12 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
     for (int kc = 0; kc < nk; ++kc) {
       cp_async_wait_pending(dist - 1);
       if (threadIdx.x == 0 && kc == 0) EGS_MARK(3);
+      if (threadIdx.x == 0 && kc < 8) EGS_MARK(200 + kc);
       if (alive) {
         split(kc, pp.tiles0 + (kc % stages) * pp.stage_bytes);
+        if (threadIdx.x == 0 && kc < 8) EGS_MARK(208 + kc);
         fence_proxy_async_smem();
+        if (threadIdx.x == 0 && kc < 8) EGS_MARK(216 + kc);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
       }
@@ -423,13 +437,27 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
       cp_async_commit();
     }
   }
-  cp_async_wait_all();
-  // all lanes of a warp must take the tcgen05.ld of the epilogue together: the decision is warp-uniform
-  alive = __all_sync(0xffffffffu, alive);
-  if (alive && nk > 0) alive = mbar_wait_warp(smem_u32(&hdr->done), 0u, pp.abort_flag, pp.status, lane);
-  if (alive) tc_fence_after();
-  if (threadIdx.x == 0) EGS_MARK(8);
-  return alive;
+  return producer_finish(pp, lane, alive);
+}
+
+// hi/lo split of one 16-byte chunk of float32 values that already sits in the hi tile.  The tensor core reads a
+// TF32 operand from the top 19 bits of each word and ignores the rest, so the raw float32 words ARE the hi
+// operand; only lo = tf32(x - trunc19(x)) has to be written, to the lo tile.
+__device__ __forceinline__ void split_store(uint32_t addr, uint32_t lo_offset, const uint4& x) {
+  const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+  uint32_t lo[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float rem = __uint_as_float(v[i]) - __uint_as_float(v[i] & 0xFFFFE000u);
+    lo[i] = (__float_as_uint(rem) + 0x1000u) & 0xFFFFE000u;   // round to tf32 (nearest, ties away) with integer ops
+  }
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr + lo_offset), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3])
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 
 // MMA lane main loop.  mma(ks, stage_base) issues the tcgen05.mma instructions of stage ks.
@@ -445,6 +473,7 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
     if (ks == 0) EGS_MARK(6);
     if (ks < 64) EGS_MARK(160 + ks);
     mma(ks, pp.tiles0 + slot * pp.stage_bytes);
+    if (ks < 8) EGS_MARK(224 + ks);
     umma_commit(smem_u32(&hdr->empty[slot]));
   }
   if (ok && pp.nk > 0) umma_commit(smem_u32(&hdr->done));
@@ -622,7 +651,45 @@ __global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_
         for (int r = cn_r0, i = 0; r < KE; r += cn_rstep, ++i, src += cn_stride) cp_async16_full(db + i * dstep, src);
       }
     };
-    const bool alive = run_producer<STRICT>(
+    // strict float32: when this thread's chunk list has the fixed 4 + 4 shape the in-place hi/lo split reads all
+    // of its chunks first (the loads pipeline) and only then splits and stores them
+    const bool split_batched = STRICT && MT == 1 && (w_nc ? nb_iters <= 4 : (cn_fast && KE % cn_rstep == 0 && KE / cn_rstep <= 4));
+    auto split_stage_batched = [&](int, uint32_t base) {
+      uint32_t dst[8];
+      bool on[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dst[i] = base + rc_dst0 + i * 4096u;
+        on[i] = true;
+        if (w_nc) {
+          dst[4 + i] = base + b_off + rc_dst0 + i * 4096u;
+          on[4 + i] = i < nb_iters && r0 + 32 * i < p.BN;
+        } else {
+          const int rr = cn_r0 + i * cn_rstep;
+          dst[4 + i] = base + b_off + cn_dst_seg + static_cast<uint32_t>(rr) * 128u +
+                       (static_cast<uint32_t>(((cn_c & 7) >> 1) ^ (rr & 3)) << 5) + (static_cast<uint32_t>(cn_c & 1) << 4);
+          on[4 + i] = rr < KE;
+        }
+      }
+      uint4 r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (on[i]) r[i] = lds16(dst[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (on[i]) split_store(dst[i], i < 4 ? a_lo_off : b_lo_off, r[i]);
+    };
+    auto issue_stage = [&](int kt, uint32_t base) {
+      if (tile_full && (kt + 1) * KE <= p.C) {
+        issue_full(kt, base);
+      } else {
+        for_each_chunk(kt, base, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : W, v ? 16u : 0u); });
+      }
+    };
+    bool alive;
+    if (split_batched) alive = run_producer<STRICT>(pp, lane, issue_stage, split_stage_batched);
+    else
+    alive = run_producer<STRICT>(
         pp, lane,
         [&](int kt, uint32_t base) {
           if (tile_full && (kt + 1) * KE <= p.C) {
@@ -675,28 +742,38 @@ __global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_
       const uint32_t b_sbo = w_nc ? 1024u : kMnSbo;
       const uint32_t b_lay = w_nc ? kSwizzle128 : kMnLayout;
       const uint32_t b_step = w_nc ? 32u : UK * 128u;
+      // descriptors differ between MMAs only in the start-address field (low 14 bits of the low word, in
+      // 16-byte units): build them once per stage and advance with an add
+      const uint64_t a_adv = 32u >> 4, b_adv = b_step >> 4;
       run_mma_lane(pp, [&](int ks, uint32_t a_hi) {
         const uint32_t b_hi = a_hi + b_off;
         const int krem = p.C - ks * KE;
         const int nkq = min(KE / UK, (krem + UK - 1) / UK);
+        uint64_t ad[MT], adl[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          ad[mt] = make_smem_desc(a_hi + mt * (kTileM * 128u), 16u, 1024u);
+          adl[mt] = STRICT ? make_smem_desc(a_hi + mt * (kTileM * 128u) + a_lo_off, 16u, 1024u) : 0ull;
+        }
+        uint64_t bd = make_smem_desc(b_hi, b_lbo, b_sbo, b_lay);
+        uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off, b_lbo, b_sbo, b_lay) : 0ull;
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
-          const uint64_t bd = make_smem_desc(b_hi + kq * b_step, b_lbo, b_sbo, b_lay);
-          const uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off + kq * b_step, b_lbo, b_sbo, b_lay) : 0ull;
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const uint32_t d = tmem_base + mt * acc_cols;
-            const uint32_t a_mt = a_hi + mt * (kTileM * 128u) + kq * 32u;
-            const uint64_t ad = make_smem_desc(a_mt, 16u, 1024u);
             if (STRICT) {
-              const uint64_t adl = make_smem_desc(a_mt + a_lo_off, 16u, 1024u);
-              umma<Elem<T>::tf32>(d, adl, bd, idesc, acc);
-              umma<Elem<T>::tf32>(d, ad, bdl, idesc, 1u);
-              umma<Elem<T>::tf32>(d, ad, bd, idesc, 1u);
+              umma<Elem<T>::tf32>(d, adl[mt], bd, idesc, acc);
+              umma<Elem<T>::tf32>(d, ad[mt], bdl, idesc, 1u);
+              umma<Elem<T>::tf32>(d, ad[mt], bd, idesc, 1u);
             } else {
-              umma<Elem<T>::tf32>(d, ad, bd, idesc, acc);
+              umma<Elem<T>::tf32>(d, ad[mt], bd, idesc, acc);
             }
+            ad[mt] += a_adv;
+            adl[mt] += a_adv;
           }
+          bd += b_adv;
+          bdl += b_adv;
         }
       });
     }
@@ -871,7 +948,38 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
       }
       b_next_kt = kt + 1;
     };
-    const bool alive = run_producer<STRICT>(
+    const bool split_batched = STRICT && KR / a_rstep <= 4 && b_fast && KR % b_rstep == 0 && KR / b_rstep <= 4;
+    auto split_stage_batched = [&](int, uint32_t base) {
+      uint32_t dst[8];
+      bool on[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int ra = a_r0 + i * a_rstep, rb = b_r0 + i * b_rstep;
+        dst[i] = base + a_dst_seg + static_cast<uint32_t>(ra) * 128u + swz(a_c, ra);
+        on[i] = ra < KR;
+        dst[4 + i] = base + b_off + b_dst_seg + static_cast<uint32_t>(rb) * 128u + swz(b_c, rb);
+        on[4 + i] = rb < KR;
+      }
+      uint4 r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (on[i]) r[i] = lds16(dst[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (on[i]) split_store(dst[i], i < 4 ? a_lo_off : b_lo_off, r[i]);
+    };
+    auto issue_stage = [&](int kt, uint32_t base) {
+      // the lean path walks b_ptr stage by stage, so it serves a prefix of consecutive full stages
+      if (tile_full && kt == b_next_kt && (kt + 1) * KR <= rows) {
+        issue_full(kt, base);
+      } else {
+        for_each_chunk(kt, base, true, [&](uint32_t dst, const char* src, bool v, bool) { cp_async16(dst, v ? src : Xs, v ? 16u : 0u); });
+      }
+    };
+    bool alive;
+    if (split_batched) alive = run_producer<STRICT>(pp, lane, issue_stage, split_stage_batched);
+    else
+    alive = run_producer<STRICT>(
         pp, lane,
         [&](int kt, uint32_t base) {
           // the lean path walks b_ptr stage by stage, so it serves a prefix of consecutive full stages
@@ -939,24 +1047,25 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
   } else {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(Elem<T>::fmt, 1u, 1u, kTileM, static_cast<uint32_t>(bn));
+      const uint64_t k_adv = (UK * 128u) >> 4;
       run_mma_lane(pp, [&](int ks, uint32_t a_hi) {
         const uint32_t b_hi = a_hi + b_off;
         const int rrem = rows - ks * KR;
         const int nkq = min(KR / UK, (rrem + UK - 1) / UK);
+        uint64_t ad = make_smem_desc(a_hi, seg_stride, kMnSbo, kMnLayout);
+        uint64_t bd = make_smem_desc(b_hi, seg_stride, kMnSbo, kMnLayout);
+        uint64_t adl = STRICT ? make_smem_desc(a_hi + a_lo_off, seg_stride, kMnSbo, kMnLayout) : 0ull;
+        uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off, seg_stride, kMnSbo, kMnLayout) : 0ull;
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
-          const uint32_t koff = kq * (UK * 128u);
-          const uint64_t ad = make_smem_desc(a_hi + koff, seg_stride, kMnSbo, kMnLayout);
-          const uint64_t bd = make_smem_desc(b_hi + koff, seg_stride, kMnSbo, kMnLayout);
           if (STRICT) {
-            const uint64_t adl = make_smem_desc(a_hi + a_lo_off + koff, seg_stride, kMnSbo, kMnLayout);
-            const uint64_t bdl = make_smem_desc(b_hi + b_lo_off + koff, seg_stride, kMnSbo, kMnLayout);
             umma<Elem<T>::tf32>(tmem_base, adl, bd, idesc, acc);
             umma<Elem<T>::tf32>(tmem_base, ad, bdl, idesc, 1u);
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
           } else {
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
           }
+          ad += k_adv; bd += k_adv; adl += k_adv; bdl += k_adv;
         }
       });
     }
@@ -1041,10 +1150,11 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   const size_t a_bytes = es * seg_stride;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t stage_bytes = (a_bytes + nseg_b * seg_stride) * (strict ? 2 : 1);
-  // split the contraction so that the grid covers the SMs about twice and no CTA owns more rows than the
+  // split the contraction so that the grid fills one wave of CTAs and no CTA owns more rows than the
   // shared-memory row table holds
   const long long tiles = static_cast<long long>((p.FG + kTileM - 1) / kTileM) * ((p.FD + bn - 1) / bn) * p.E;
-  long long want = (2 * kSmCount + tiles - 1) / tiles;
+  // as many row ranges as still fit in one wave of CTAs (one CTA per SM in strict mode, else two)
+  long long want = (static_cast<long long>(kSmCount) * (strict ? 1 : 2)) / tiles;
   const long long min_splits = (p.M + kMaxRowsPerSplit - 1) / kMaxRowsPerSplit;
   if (want < min_splits) want = min_splits;
   const long long max_splits = (p.M + kr - 1) / kr;
