@@ -19,7 +19,7 @@ PATH_AUTO, PATH_GENERIC, PATH_TENSOR = 0, 1, 2
 W_CN, W_NC = 0, 1
 DW_GATHERED_ROWS, DW_DIRECT_ROWS = 0, 1
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TOO_LARGE = range(6)
-STATUS_INDEX_OUT_OF_RANGE, STATUS_PIPELINE_TIMEOUT = 1, 2
+STATUS_INDEX_OUT_OF_RANGE, STATUS_PIPELINE_TIMEOUT, STATUS_INTERNAL = 1, 2, 4
 
 EXPORTS = (
     "egs_version", "egs_status_string", "egs_last_cuda_error", "egs_gather_gemm", "egs_gemm_scatter",

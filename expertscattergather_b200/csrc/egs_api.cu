@@ -1,6 +1,7 @@
 // extern "C" entry points of libegs_b200.so: argument validation, path selection, launches.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "egs_internal.cuh"
@@ -135,6 +136,10 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     const double act_bytes = static_cast<double>(d.B) * d.T * (scatter ? d.N * 4.0 : d.C * static_cast<double>(elem_size(dtype)));
     const double w_bytes = static_cast<double>(d.E) * d.C * d.N * elem_size(dtype);
     p.expert_fastest = (act_bytes > 96e6 && w_bytes < 64e6 && (d.B * d.K + 127) / 128 <= 65535) ? 1 : 0;
+    {
+      static const char* order_env = getenv("EGS_B200_EXPERT_FASTEST");   // tuning aid: force the grid order
+      if (order_env && (d.B * d.K + 127) / 128 <= 65535) p.expert_fastest = atoi(order_env) ? 1 : 0;
+    }
     const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
     err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
   } else {

@@ -45,7 +45,8 @@ constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kThreads = kProducerThreads + 32;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kHeaderBytes = 3072;
+constexpr uint32_t kHeaderBytes = 3072;       // row kernel: barriers + two row tables
+constexpr uint32_t kHeaderBytesD = 1024;      // weight-gradient kernel: barriers only (the row tables are unused)
 constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 clocks
 
 constexpr int kMaxRowsPerSplit = 4096;   // operator D: contraction rows one CTA may own (row table in smem)
@@ -284,6 +285,49 @@ __device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, i
   }
   __syncwarp();
 }
+// Same transpose for a 32-row x 64-column block (8 KB tile): every lane ends up with 8 consecutive columns of
+// one row, so 8 lanes cover 64 columns - 128 contiguous bytes of a 16-bit row per instruction.
+//   emit(row_in_block, first_column, x[8]) is called 8 times per lane.
+template <class Emit>
+__device__ __forceinline__ void warp_block_emit64(uint32_t taddr, uint32_t tile, int lane, Emit&& emit) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t v[32];
+    tmem_ld32(taddr + h * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + lane * 256u + (static_cast<uint32_t>((h * 8 + j) ^ (lane & 7)) << 4)),
+                   "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                   : "memory");
+  }
+  __syncwarp();
+  const int j = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    uint32_t x[8];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(x[4 * q]), "=r"(x[4 * q + 1]), "=r"(x[4 * q + 2]), "=r"(x[4 * q + 3])
+                   : "r"(tile + row * 256u + (static_cast<uint32_t>((2 * j + q) ^ (row & 7)) << 4))
+                   : "memory");
+    emit(row, j * 8, x);
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void red8(__nv_bfloat16* dst, const uint32_t (&x)[8]) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(pack2(dst, x[0], x[1])),
+               "r"(pack2(dst, x[2], x[3])), "r"(pack2(dst, x[4], x[5])), "r"(pack2(dst, x[6], x[7]))
+               : "memory");
+}
+__device__ __forceinline__ void red8(__half* dst, const uint32_t (&x)[8]) {
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(pack2(dst, x[0], x[1])),
+               "r"(pack2(dst, x[2], x[3])), "r"(pack2(dst, x[4], x[5])), "r"(pack2(dst, x[6], x[7]))
+               : "memory");
+}
+__device__ __forceinline__ void red8(float*, const uint32_t (&)[8]) {}   // never taken: direct adds are 16-bit only
 __device__ __forceinline__ void red4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
   asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(__uint_as_float(x0)), "f"(__uint_as_float(x1)),
                "f"(__uint_as_float(x2)), "f"(__uint_as_float(x3))
@@ -309,10 +353,9 @@ __device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
   return c;
 }
 
-__device__ __forceinline__ char* aligned_smem(unsigned char* raw) {
-  const uint32_t a = smem_u32(raw);
-  return reinterpret_cast<char*>(raw) + ((1024u - (a & 1023u)) & 1023u);
-}
+// The dynamic shared memory is declared 1024-byte aligned (the swizzle atoms need it).  Should a launch ever
+// hand out a differently aligned base, the CTA refuses to work and reports EGS_STATUS_INTERNAL.
+__device__ __forceinline__ bool smem_misaligned(const void* raw) { return (smem_u32(raw) & 1023u) != 0u; }
 
 // Optional phase trace (compile with -DEGS_TRACE): CTA (0,0,0) records globaltimer stamps of its phases.
 #ifdef EGS_TRACE
@@ -356,6 +399,10 @@ __device__ __forceinline__ uint32_t pipe_setup(const Pipe& pp, uint32_t full_cou
     // from costing one wait limit per wave of CTAs).
     hdr->abort_flag =
         (pp.status && (*reinterpret_cast<volatile int32_t*>(pp.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+    if (smem_misaligned(hdr)) {
+      hdr->abort_flag = 1u;
+      if (pp.status) atomicOr(pp.status, EGS_STATUS_INTERNAL);
+    }
   }
   if (warp == kProducerWarps) {
     tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
@@ -501,8 +548,8 @@ __global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_
   constexpr bool kMn32 = (ES == 4);   // MN-major 32-bit tiles use the 32-byte-granule swizzle
   constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
   constexpr uint32_t kMnSbo = kMn32 ? 512u : 1024u;
-  extern __shared__ unsigned char smem_raw[];
-  char* smem = aligned_smem(smem_raw);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  char* smem = reinterpret_cast<char*>(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -714,6 +761,23 @@ __global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_
       // 16-bit S: the planning flag says whether to add into the float32 rows or straight into the output
       const bool direct16 = SCATTER && ES == 2 && p.plan != nullptr && *p.plan == 0;
       const int nblk = (bn + 31) >> 5;
+      // direct 16-bit adds go out in 64-column blocks (128-byte row segments) when the ring has room for the
+      // eight 8 KB transpose tiles and the tile width is a multiple of 64
+      const bool wide16 = direct16 && (bn % 64 == 0) && (pp.stages * pp.stage_bytes >= 8u * 8192u);
+      if (wide16) {
+        const uint32_t tile8 = pp.tiles0 + static_cast<uint32_t>(warp) * 8192u;
+        for (int mt = 0; mt < MT; ++mt) {
+          for (int c = half; c < (bn >> 6); c += 2) {
+            const int col0 = n0 + c * 64;
+            warp_block_emit64(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + mt * acc_cols + static_cast<uint32_t>(c * 64), tile8,
+                              lane, [&](int row, int cj, const uint32_t (&x)[8]) {
+                                const int ro = hdr->row_o[mt * kTileM + lg * 32 + row];
+                                const int col = col0 + cj;
+                                if (ro >= 0 && col < p.N) red8(out + static_cast<long long>(ro) * p.N + col, x);
+                              });
+          }
+        }
+      } else
       for (int mt = 0; mt < MT; ++mt) {
         for (int c = half; c < nblk; c += 2) {
           const int col0 = n0 + c * 32;
@@ -799,10 +863,10 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
   constexpr bool kMn32 = (ES == 4);     // MN-major 32-bit tiles use the 32-byte-granule swizzle
   constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
   constexpr uint32_t kMnSbo = kMn32 ? 512u : 1024u;
-  extern __shared__ unsigned char smem_raw[];
-  char* smem = aligned_smem(smem_raw);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  char* smem = reinterpret_cast<char*>(smem_raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
-  int* row_tok = reinterpret_cast<int*>(smem + kHeaderBytes);     // [rows_per_split] token row or -1
+  int* row_tok = reinterpret_cast<int*>(smem + kHeaderBytesD);    // [rows_per_split] token row or -1
   const uint32_t table_bytes = (static_cast<uint32_t>(p.rows_per_split) * 4u + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -828,7 +892,7 @@ __global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kerne
   pp.hdr = hdr;
   pp.abort_flag = &hdr->abort_flag;
   pp.status = p.status;
-  pp.tiles0 = smem_u32(smem) + kHeaderBytes + table_bytes;
+  pp.tiles0 = smem_u32(smem) + kHeaderBytesD + table_bytes;
   pp.stage_bytes = (a_bytes + b_bytes) * (STRICT ? 2u : 1u);
   pp.stages = p.stages;
   pp.nk = (rows + KR - 1) / KR;
@@ -1122,7 +1186,7 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   p.BN = bn;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t b_bytes = (p.w_layout == EGS_W_NC) ? static_cast<size_t>(bn) * 128 : nseg_b * ke * 128;
-  const size_t fixed = 1024 + kHeaderBytes;
+  const size_t fixed = kHeaderBytes;
   const long long n_tiles = (p.N + bn - 1) / bn;
   // 256-row CTAs (two accumulators): when the grid still fills the SMs at least once, the contraction is long
   // enough for the deeper ring to matter, and the two accumulators fit in tensor memory
@@ -1167,7 +1231,7 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   p.splits = static_cast<int>((p.M + rows - 1) / rows);
   if (p.splits < 1) p.splits = 1;
   const size_t table_bytes = (static_cast<size_t>(rows) * 4 + 1023) & ~static_cast<size_t>(1023);
-  const size_t fixed = 1024 + kHeaderBytes + table_bytes;
+  const size_t fixed = kHeaderBytesD + table_bytes;
   p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, !strict);
   return fixed + p.stages * stage_bytes;
 }

@@ -101,6 +101,8 @@ def check_status(device=None) -> None:
                 msgs.append("an Ind value outside [0, T) was met (slot skipped)")
             if v & _lib.STATUS_PIPELINE_TIMEOUT:
                 msgs.append("a bounded wait inside a tensor-core kernel ran out (results invalid)")
+            if v & _lib.STATUS_INTERNAL:
+                msgs.append("a tensor-core kernel found its shared memory misaligned and did no work (results invalid)")
             raise RuntimeError(f"egs kernels on cuda:{idx} reported: " + "; ".join(msgs))
 
 

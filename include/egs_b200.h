@@ -55,7 +55,8 @@ enum {
 /* Bits a kernel may OR into the optional device status word (int32, caller-owned, may be NULL). */
 enum {
   EGS_STATUS_INDEX_OUT_OF_RANGE = 1,  /* an Ind value outside [0,T) was met; that slot was skipped */
-  EGS_STATUS_PIPELINE_TIMEOUT = 2     /* a bounded wait inside a kernel ran out; results are invalid */
+  EGS_STATUS_PIPELINE_TIMEOUT = 2,    /* a bounded wait inside a kernel ran out; results are invalid */
+  EGS_STATUS_INTERNAL = 4             /* a kernel found its shared memory misaligned and did no work */
 };
 
 typedef struct egs_dims {
