@@ -540,7 +540,7 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
 // accumulators are fed from the same W tile, which cuts the bytes loaded per flop by a third and lets a
 // three-stage ring of one CTA per SM cover the load latency that two 2-stage CTAs cannot.
 template <typename T, bool STRICT, bool SCATTER, int MT>
-__global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_rowgemm_kernel(RowGemmParams p) {
+__global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kernel(RowGemmParams p) {
   constexpr int kRows = kTileM * MT;        // expert rows per CTA
   constexpr int ES = sizeof(T);
   constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
@@ -854,7 +854,7 @@ __global__ void __launch_bounds__(kThreads, (STRICT || MT == 2) ? 1 : 2) tensor_
 //   splits == 1: the tile is stored in the output dtype; splits > 1: red.global.add.f32 into p.acc
 // ------------------------------------------------------------------------------------------------
 template <typename T, bool STRICT>
-__global__ void __launch_bounds__(kThreads, STRICT ? 1 : 2) tensor_dweight_kernel(DWeightParams p) {
+__global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightParams p) {
   constexpr int ES = sizeof(T);
   constexpr int KR = 128 / ES;          // contraction rows per stage (4 MMAs of UK rows)
   constexpr int UK = 32 / ES;           // contraction rows per tcgen05.mma
@@ -1183,6 +1183,11 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   int bn = (p.N + 15) & ~15;
   const int cap = tile_n_cap(strict ? 128 : 256);
   if (bn > cap) bn = cap;
+  // strict float32 doubles every tile (hi + lo): when the grid is larger than one wave, 64-wide tiles keep a
+  // 2-stage ring under half an SM's shared memory so that two CTAs share an SM
+  if (strict && bn > 64 &&
+      static_cast<long long>((p.M + kTileM - 1) / kTileM) * ((p.N + bn - 1) / bn) * p.E > kSmCount)
+    bn = 64;
   p.BN = bn;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   const size_t b_bytes = (p.w_layout == EGS_W_NC) ? static_cast<size_t>(bn) * 128 : nseg_b * ke * 128;
@@ -1198,7 +1203,7 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   const size_t a_bytes = static_cast<size_t>(kTileM) * p.row_tiles * 128;
   const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
   const long long ctas = static_cast<long long>((p.M + kTileM * p.row_tiles - 1) / (kTileM * p.row_tiles)) * n_tiles * p.E;
-  p.stages = pick_stages(fixed, stage_bytes, ctas, !strict && p.row_tiles == 1);
+  p.stages = pick_stages(fixed, stage_bytes, ctas, p.row_tiles == 1);
   return fixed + p.stages * stage_bytes;
 }
 
@@ -1207,7 +1212,7 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int kr = 128 / es;
   int bn = (p.FD + 15) & ~15;
-  const int cap = tile_n_cap(strict ? 128 : 256);
+  const int cap = tile_n_cap(strict ? 64 : 256);   // strict: 64-wide tiles so that two CTAs share an SM
   if (bn > cap) bn = cap;
   p.BN = bn;
   const size_t seg_stride = static_cast<size_t>(kr) * 128;
@@ -1217,8 +1222,8 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   // split the contraction so that the grid fills one wave of CTAs and no CTA owns more rows than the
   // shared-memory row table holds
   const long long tiles = static_cast<long long>((p.FG + kTileM - 1) / kTileM) * ((p.FD + bn - 1) / bn) * p.E;
-  // as many row ranges as still fit in one wave of CTAs (one CTA per SM in strict mode, else two)
-  long long want = (static_cast<long long>(kSmCount) * (strict ? 1 : 2)) / tiles;
+  // as many row ranges as still fit in one wave of CTAs (two CTAs per SM)
+  long long want = (static_cast<long long>(kSmCount) * 2) / tiles;
   const long long min_splits = (p.M + kMaxRowsPerSplit - 1) / kMaxRowsPerSplit;
   if (want < min_splits) want = min_splits;
   const long long max_splits = (p.M + kr - 1) / kr;
@@ -1232,7 +1237,7 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   if (p.splits < 1) p.splits = 1;
   const size_t table_bytes = (static_cast<size_t>(rows) * 4 + 1023) & ~static_cast<size_t>(1023);
   const size_t fixed = kHeaderBytesD + table_bytes;
-  p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, !strict);
+  p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, true);
   return fixed + p.stages * stage_bytes;
 }
 

@@ -40,12 +40,30 @@ def _gather_forward(X, W, Ind, out_dtype):
     return ops.gather_gemm(X, W, Ind, w_layout="cn")
 
 
+def _weight_grad_on_side_stream(Xsrc, Ysrc, Ind, out_layout):
+    """Enqueues operator D on the helper stream (it is independent of the dX / dY kernel of the same backward
+    call, and the two co-reside on the SMs); the caller joins with ``_join_side``."""
+    dev = Xsrc.device
+    main = torch.cuda.current_stream(dev)
+    side = ops.side_stream(dev)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        grad_W = ops.dweight(Xsrc, Ysrc, Ind, out_layout=out_layout)
+        grad_W.record_stream(main)
+    return grad_W
+
+
+def _join_side(t):
+    torch.cuda.current_stream(t.device).wait_stream(ops.side_stream(t.device))
+
+
 def _gather_backward(X, W, Ind, grad_output, out_dtype):
     # dX = scatter(dY @ W_g^T), dW_g = gather(X)^T @ dY        (reference: egs/triton_kernels.py:400-441)
     T = X.shape[1]
     grad_output = grad_output.contiguous()
+    grad_W = _weight_grad_on_side_stream(X, grad_output, Ind, "gathered_rows")
     grad_X = ops.gemm_scatter(grad_output, W, Ind, T, w_layout="nc")
-    grad_W = ops.dweight(X, grad_output, Ind, out_layout="gathered_rows")
+    _join_side(grad_X)
     return grad_X, grad_W
 
 
@@ -57,8 +75,9 @@ def _scatter_forward(Y, W, Ind, T, out_dtype):
 def _scatter_backward(Y, W, Ind, grad_X, out_dtype):
     # dY = gather(dOut) @ W_s^T, dW_s = Y^T @ gather(dOut)     (reference: egs/triton_kernels.py:483-525)
     grad_X = grad_X.contiguous()
+    grad_W = _weight_grad_on_side_stream(grad_X, Y, Ind, "direct_rows")
     grad_Y = ops.gather_gemm(grad_X, W, Ind, w_layout="nc")
-    grad_W = ops.dweight(grad_X, Y, Ind, out_layout="direct_rows")
+    _join_side(grad_Y)
     return grad_Y, grad_W
 
 

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gather_gemm", "gemm_scatter", "dweight", "set_precision", "get_precision", "set_path", "get_path",
+__all__ = ["gather_gemm", "gemm_scatter", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
            "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
@@ -104,6 +104,32 @@ def check_status(device=None) -> None:
             if v & _lib.STATUS_INTERNAL:
                 msgs.append("a tensor-core kernel found its shared memory misaligned and did no work (results invalid)")
             raise RuntimeError(f"egs kernels on cuda:{idx} reported: " + "; ".join(msgs))
+
+
+_side_streams: dict[int, "torch.cuda.Stream"] = {}
+
+
+def side_stream(device) -> "torch.cuda.Stream":
+    """A per-device helper stream on which independent work of one step (zero fills, weight gradients) is
+    enqueued next to the main chain.  Users fork with ``side.wait_stream(current)`` and join with
+    ``current.wait_stream(side)``."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _side_streams.get(idx)
+    if st is None:
+        st = torch.cuda.Stream(torch.device("cuda", idx))
+        _side_streams[idx] = st
+    return st
+
+
+def fill_zero(t: torch.Tensor) -> torch.Tensor:
+    """Zero-fills a contiguous CUDA tensor with the library's fill kernel on the current stream."""
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("fill_zero needs a contiguous CUDA tensor")
+    with torch.cuda.device(t.device):
+        rc = _lib.load().egs_fill_zero(t.data_ptr(), t.numel() * t.element_size(), _stream_ptr(t.device))
+    _lib.check(rc, "egs_fill_zero")
+    return t
 
 
 def launch_count() -> int:

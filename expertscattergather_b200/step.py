@@ -17,21 +17,63 @@ __all__ = ["train_step"]
 
 
 def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.Tensor, G: torch.Tensor,
-               on_weight_grad: Optional[Callable[[str, torch.Tensor], None]] = None) -> dict:
+               on_weight_grad: Optional[Callable[[str, torch.Tensor], None]] = None, overlap: bool = True) -> dict:
     """X [B,T,I], Wg [E,I,J], Ws [E,J,I], Ind [B,E,K], G [B,T,I] (the gradient of the loss w.r.t. Out).
 
     Returns Y, Out, dY, dX, dWg, dWs.  Equivalent to
     ``Y = ExpertGather(X, Ind); Out = ExpertScatter(Y, Ind, T); (Out*G).sum().backward()``.
+
+    With ``overlap`` the work that is off the critical chain G -> S -> dY -> dX runs on a side stream: the zero
+    fills of Out and dX (float32 tensors; 16-bit outputs are initialised by the scatter's own planning step) and
+    the two weight-gradient kernels, each started as soon as its inputs exist.  ``on_weight_grad`` is called on
+    that side stream right after the gradient has been enqueued.
     """
     T = X.shape[1]
-    Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                 # gather forward
-    Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn")           # scatter forward
-    dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                # scatter backward: dY
-    dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")         # scatter backward: dW_s
-    if on_weight_grad is not None:
-        on_weight_grad("Ws", dWs)
-    dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc")           # gather backward: dX
-    dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")      # gather backward: dW_g
-    if on_weight_grad is not None:
-        on_weight_grad("Wg", dWg)
+    if not overlap:
+        Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                 # gather forward
+        Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn")           # scatter forward
+        dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                # scatter backward: dY
+        dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")         # scatter backward: dW_s
+        if on_weight_grad is not None:
+            on_weight_grad("Ws", dWs)
+        dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc")           # gather backward: dX
+        dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")      # gather backward: dW_g
+        if on_weight_grad is not None:
+            on_weight_grad("Wg", dWg)
+        return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
+
+    dev = X.device
+    main = torch.cuda.current_stream(dev)
+    side = ops.side_stream(dev)
+    prefill = X.dtype == torch.float32
+    Out = dX = None
+    side.wait_stream(main)                                             # fork
+    if prefill:
+        Out = torch.empty((X.shape[0], T, Ws.shape[2]), device=dev, dtype=X.dtype)
+        dX = torch.empty_like(X, memory_format=torch.contiguous_format)
+        with torch.cuda.stream(side):
+            ops.fill_zero(Out)
+            ops.fill_zero(dX)
+        fills_done = side.record_event()
+    Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                     # gather forward
+    if prefill:
+        main.wait_event(fills_done)
+    Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn", out=Out)      # scatter forward (adds into zeros)
+    fwd_done = main.record_event()
+    with torch.cuda.stream(side):                                      # scatter backward: dW_s, next to dY
+        side.wait_event(fwd_done)                                      # the backward pass starts after the forward
+        dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")
+        dWs.record_stream(main)
+        if on_weight_grad is not None:
+            on_weight_grad("Ws", dWs)
+    dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                    # scatter backward: dY
+    dy_ready = main.record_event()
+    with torch.cuda.stream(side):                                      # gather backward: dW_g, next to dX
+        side.wait_event(dy_ready)
+        dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
+        dWg.record_stream(main)
+        if on_weight_grad is not None:
+            on_weight_grad("Wg", dWg)
+    dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc", out=dX)       # gather backward: dX
+    main.wait_stream(side)                                             # join
     return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
