@@ -25,6 +25,18 @@ sys.path.insert(0, ROOT)
 
 from expertscattergather_b200 import workloads as wl  # noqa: E402
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of one operator call, from the ncu
+# captures summarised under profiles/ (bytes per routed slot of the captured case; scaled by the slots of the run).
+NCU_TRAFFIC_PER_SLOT = {
+    ("scatter_fwd", "cfg1-T16384"): (75.4e6 + 13.6e6) / 16384,      # fill_zero + scatter kernel
+    ("gather_bwd_dX", "cfg1-T16384"): (75.1e6 + 13.6e6) / 16384,
+    ("scatter_fwd", "cfg4"): (331.5e6 + 113.5e6) / 262144,          # captured at B=64
+    ("gather_bwd_dX", "cfg4"): (327.9e6 + 114.4e6) / 262144,
+    ("scatter_bwd_dW", "cfg4"): (370.4e6 + 23.7e6) / 262144,
+    ("gather_bwd_dW", "cfg4"): (368.6e6 + 23.3e6) / 262144,
+    ("gather_fwd", "cfg4"): (265.5e6 + 113.7e6) / 262144,
+    ("scatter_bwd_dY", "cfg4"): (272.8e6 + 110.5e6) / 262144,
+}
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "gather+scatter fwd+bwd routed tokens/s"
 
@@ -285,7 +297,6 @@ def main():
         run_step()
         stops[i].record()
     barrier()
-    clocks = sampler.stop()
     step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
     total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -343,6 +354,7 @@ def main():
             fl, by = op_work(w, b, U, op)
             breakdown.append({"pass": w.name, "op": op, "ms": ms, "flops": fl, "bytes": by})
         del Y, dY
+    clocks = sampler.stop()      # sampled from the start of the timed steps to the end of the per-operator timing
     dom = max(breakdown, key=lambda r: r["ms"])
     if passes[0].dtype == torch.float32:
         # no TF32 figure in MEASURED_PEAKS.json: measure a TF32 torch.matmul the same way (8192^3, best of 10)
@@ -368,8 +380,12 @@ def main():
     else:
         ach = dom["flops"] / (dom["ms"] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": tc_peak, "unit": "TFLOP/s", "frac": ach / tc_peak}
-    roof.update({"traffic": None, "kernel": f'{dom["op"]} @ {dom["pass"]}', "peak_source": peaks["source"],
-                 "ms_per_launch": dom["ms"]})
+    dom_w = next(w for w in passes if w.name == dom["pass"])
+    dom_b = shard_B[passes.index(dom_w)]
+    per_slot = NCU_TRAFFIC_PER_SLOT.get((dom["op"], dom["pass"].split(" ")[0]))
+    traffic = per_slot * dom_b * dom_w.E * dom_w.K if per_slot is not None else None
+    roof.update({"traffic": traffic, "kernel": f'{dom["op"]} @ {dom["pass"]}', "peak_source": peaks["source"],
+                 "ms_per_launch": dom["ms"], "algorithmic": dom["bytes"] if roof["bound"] == "hbm" else dom["flops"]})
     # whole-step floor for context
     alg = [wl.algorithmic_work(w, Ind=h["Ind"], B=b) for w, h, b in zip(passes, host, shard_B)]
     step_floor_ms = sum(max(a["bytes"] / (peaks["hbm_gbs"] * 1e9), a["flops"] / (tc_peak * 1e12)) for a in alg) * 1e3
@@ -435,7 +451,8 @@ def main():
             "config": {"workload": name, "passes": [f"{w.name}: B={w.B} T={w.T} E={w.E} K={w.K} I={w.I} J={w.J}" for w in passes],
                        "routed_tokens_per_step": tokens_per_step, "parallelism": f"dp{world} (batch-sharded, dW all-reduce)",
                        "l2": "flush buffer written between steps" if flush_buf is not None else "inputs larger than L2",
-                       "cuda_graph": bool(graph is not None), "precision": ops.get_precision()},
+                       "cuda_graph": bool(graph is not None), "precision": ops.get_precision(),
+                       "streams": "zero fills and weight gradients on a side stream next to the G->S->dY->dX chain"},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
             "roofline": roof,
