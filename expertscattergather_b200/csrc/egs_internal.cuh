@@ -56,6 +56,7 @@ struct RowGemmParams {
   int stages;         // tensor path: pipeline depth
   int expert_fastest; // tensor path: grid order (1: experts vary fastest, row tiles slowest)
   int row_tiles;      // tensor path: 128-row accumulator tiles per CTA (1 or 2)
+  int persistent;     // tensor path: 1 = persistent warp-specialised variant
 };
 
 struct DWeightParams {

@@ -273,17 +273,18 @@ __device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, i
                  : "memory");
   __syncwarp();
   const int j = lane & 7;
+  uint32_t x[8][4];
 #pragma unroll
-  for (int it = 0; it < 8; ++it) {
+  for (int it = 0; it < 8; ++it) {      // all reads first, so that their latencies overlap
     const int row = it * 4 + (lane >> 3);
-    uint32_t x[4];
     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3])
+                 : "=r"(x[it][0]), "=r"(x[it][1]), "=r"(x[it][2]), "=r"(x[it][3])
                  : "r"(tile + row * 128u + (static_cast<uint32_t>(j ^ (row & 7)) << 4))
                  : "memory");
-    emit(row, j * 4, x[0], x[1], x[2], x[3]);
   }
-  __syncwarp();
+  __syncwarp();                         // the tile may be overwritten from here on
+#pragma unroll
+  for (int it = 0; it < 8; ++it) emit(it * 4 + (lane >> 3), j * 4, x[it][0], x[it][1], x[it][2], x[it][3]);
 }
 // Same transpose for a 32-row x 64-column block (8 KB tile): every lane ends up with 8 consecutive columns of
 // one row, so 8 lanes cover 64 columns - 128 contiguous bytes of a 16-bit row per instruction.
@@ -847,6 +848,343 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
 }
 
 // ------------------------------------------------------------------------------------------------
+// Operators G and S, persistent variant.   grid = min(#SMs, row blocks) CTAs of 17 warps.
+//   A row block is one (expert, 128 expert rows) pair; a CTA walks row blocks blockIdx.x, +gridDim.x, ... and, inside
+//   a row block, all N tiles.  The stage ring never drains between tiles, the accumulator is double-buffered in
+//   tensor memory, and dedicated epilogue warps drain tile t while the tensor core works on tile t+1:
+//     warps 0..7   producers (cp.async row gathers, hardware arrive on full[s])
+//     warps 8..15  epilogue  (tcgen05.ld -> shared-memory transpose -> stores / red.global.add)
+//     warp  16     TMEM allocation; one lane issues tcgen05.mma and commits to empty[s] and acc_full[b]
+//   Short contractions with wide outputs (the scatter operator) are where this matters: with one CTA per tile
+//   their time goes into the per-tile latency chain (set-up, first loads, a 2-stage ring, an epilogue nothing
+//   overlaps), not into tensor work or atomics.
+//   No shared row tables: every producer thread looks up the token rows of the four tile rows it copies, every
+//   epilogue warp those of its 32 lanes, so the roles never have to meet at a CTA-wide barrier after set-up.
+//   Non-strict arithmetic only (bf16 / fp16 / single TF32 product).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPersistMaxEpilogueWarps = 8;
+constexpr uint32_t kPersistHeaderBytes = 1024;
+// Warp split: 8 producer + 8 epilogue warps.  (Measured: 4 producer warps starve the ring; 16 epilogue warps do not
+// help because the transpose tiles then cost a ring stage and shared-memory bandwidth is what they compete for.)
+template <bool SCATTER> struct PersistShape {
+  static constexpr int kProducerWarps = 8;
+  static constexpr int kEpilogueWarps = 8;
+  static constexpr int kThreads = (kProducerWarps + kEpilogueWarps + 1) * 32;
+};
+
+struct __align__(16) PersistHeader {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long acc_full[2];
+  unsigned long long acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+static_assert(sizeof(PersistHeader) <= kPersistHeaderBytes, "header does not fit");
+
+struct RowBlock {
+  int e, m0;
+};
+__device__ __forceinline__ RowBlock row_block_of(const RowGemmParams& p, int rb, int m_tiles) {
+  RowBlock r;
+  if (p.expert_fastest) {
+    r.e = rb % p.E;
+    r.m0 = (rb / p.E) * kTileM;
+  } else {
+    r.m0 = (rb % m_tiles) * kTileM;
+    r.e = rb / m_tiles;
+  }
+  return r;
+}
+// Source / destination row of expert row m of expert e (-1 = masked).  G: source token row, destination slot row;
+// S: source slot row, destination token row.
+template <bool SCATTER>
+__device__ __forceinline__ void lookup_rows(const RowGemmParams& p, int e, int m, int& src_row, int& dst_row, bool report) {
+  src_row = -1;
+  dst_row = -1;
+  if (m >= p.M) return;
+  const int b = m / p.K, k = m - b * p.K;
+  const int slot = (b * p.E + e) * p.K + k;
+  const long long t = load_index(p.Ind, p.index_dtype, slot);
+  if (t >= 0 && t < p.T) {
+    const int tok = b * p.T + static_cast<int>(t);
+    src_row = SCATTER ? slot : tok;
+    dst_row = SCATTER ? tok : slot;
+  } else {
+    if (report && p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+    if (!SCATTER) dst_row = slot;      // gather: the row is still written (zeros)
+  }
+}
+
+template <typename T, bool SCATTER>
+__global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_rowgemm_persistent_kernel(RowGemmParams p) {
+  constexpr int kPersistProducerWarps = PersistShape<SCATTER>::kProducerWarps;
+  constexpr int kPersistEpilogueWarps = PersistShape<SCATTER>::kEpilogueWarps;
+  constexpr int PT = kPersistProducerWarps * 32;     // producer threads
+  constexpr int RS = PT / 8;                         // tile rows covered by one pass of the producers (8 threads per row)
+  constexpr int ES = sizeof(T);
+  constexpr int KE = 128 / ES;        // contraction elements per stage (one 128-byte segment)
+  constexpr int UK = 32 / ES;         // contraction elements per tcgen05.mma
+  constexpr bool kMn32 = (ES == 4);
+  constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
+  constexpr uint32_t kMnSbo = kMn32 ? 512u : 1024u;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  PersistHeader* hdr = reinterpret_cast<PersistHeader*>(smem_raw);
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t xpose0 = smem0 + kPersistHeaderBytes;                             // 8 transpose tiles of 4 KB
+  const uint32_t tiles0 = xpose0 + kPersistMaxEpilogueWarps * 4096u;               // stage ring
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) EGS_MARK(0);
+  const bool w_nc = (p.w_layout == EGS_W_NC);
+  const int m_tiles = (p.M + kTileM - 1) / kTileM;
+  const int n_tiles = (p.N + p.BN - 1) / p.BN;
+  const int row_blocks = p.E * m_tiles;
+  const int stages = p.stages;
+  const int nk = (p.C + KE - 1) / KE;
+  const uint32_t a_bytes = kTileM * 128u;
+  const int nseg_b = (p.BN * ES + 127) / 128;
+  const uint32_t b_bytes = w_nc ? static_cast<uint32_t>(p.BN) * 128u : static_cast<uint32_t>(nseg_b) * KE * 128u;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  const uint32_t b_off = a_bytes;
+  const uint32_t acc_cols = tmem_cols_for(p.BN);
+  const uint32_t tmem_cols = 2u * acc_cols;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  // ---- set-up: barriers, abort check, tensor memory (the only CTA-wide barrier before the exit) ----
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), kPersistProducerWarps * 32);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&hdr->acc_full[b]), 1);
+      mbar_init(smem_u32(&hdr->acc_empty[b]), kPersistEpilogueWarps);
+    }
+    fence_mbar_init();
+    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+    if (smem_misaligned(smem_raw)) {
+      hdr->abort_flag = 1u;
+      if (p.status) atomicOr(p.status, EGS_STATUS_INTERNAL);
+    }
+  }
+  const int mma_warp = kPersistProducerWarps + kPersistEpilogueWarps;
+  if (warp == mma_warp) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+  const bool run = (hdr->abort_flag == 0u);
+
+  if (!run) {
+    // fall through to the common exit
+  } else if (warp < kPersistProducerWarps) {
+    // =========================== producers ===========================
+    const char* A = static_cast<const char*>(p.A);
+    const char* W = static_cast<const char*>(p.W);
+    const long long row_bytes_a = static_cast<long long>(p.C) * ES;
+    const long long row_bytes_w = static_cast<long long>(p.N) * ES;
+    const int cc = tid & 7, r0 = tid >> 3;
+    const uint32_t rc_dst0 = static_cast<uint32_t>(r0) * 128u + (static_cast<uint32_t>(cc ^ (r0 & 7)) << 4);
+    const int nb_iters = (p.BN + RS - 1) / RS;
+    const long long nc_stride = static_cast<long long>(RS) * row_bytes_a;
+    const int cpr = nseg_b * 8;
+    const bool cn_fast = (PT % cpr) == 0;
+    const int cn_c = tid % cpr, cn_r0 = tid / cpr, cn_rstep = PT / cpr;
+    const long long cn_stride = static_cast<long long>(cn_rstep) * row_bytes_w;
+    const uint32_t cn_dst_seg = static_cast<uint32_t>(cn_c >> 3) * (KE * 128u);
+    auto mn_swz = [](int c, int r) -> uint32_t {
+      return kMn32 ? ((static_cast<uint32_t>(((c & 7) >> 1) ^ (r & 3)) << 5) + (static_cast<uint32_t>(c & 1) << 4))
+                   : (static_cast<uint32_t>((c & 7) ^ (r & 7)) << 4);
+    };
+    const uint32_t cn_dst0 = cn_dst_seg + static_cast<uint32_t>(cn_r0) * 128u + mn_swz(cn_c, cn_r0);
+    const bool cn_shape_ok = cn_fast && (KE % cn_rstep == 0) && (cn_rstep % 8 == 0 || kMn32);
+    bool alive = true;
+    int g = 0;                                   // stages issued so far by this CTA (ring position)
+    for (int rb = blockIdx.x; rb < row_blocks && alive; rb += gridDim.x) {
+      const RowBlock blk = row_block_of(p, rb, m_tiles);
+      const char* a_src[kTileM / RS];
+      uint32_t a_mask = 0;
+#pragma unroll
+      for (int i = 0; i < kTileM / RS; ++i) {
+        int src_row, dst_row;
+        lookup_rows<SCATTER>(p, blk.e, blk.m0 + r0 + RS * i, src_row, dst_row, false);
+        a_src[i] = A + (src_row >= 0 ? static_cast<long long>(src_row) * row_bytes_a : 0ll) + cc * 16;
+        if (src_row >= 0) a_mask |= 1u << i;
+      }
+      const bool a_full = (a_mask == (1u << (kTileM / RS)) - 1u);
+      for (int nt = 0; nt < n_tiles && alive; ++nt) {
+        const int n0 = nt * p.BN;
+        const char* nc_src0 = W + (static_cast<long long>(blk.e) * p.N + n0 + r0) * row_bytes_a + cc * 16;
+        uint32_t nc_mask = 0;
+        for (int i = 0; i < nb_iters; ++i)
+          if (r0 + RS * i < p.BN && n0 + r0 + RS * i < p.N) nc_mask |= 1u << i;
+        const char* cn_src0 =
+            W + (static_cast<long long>(blk.e) * p.C + cn_r0) * row_bytes_w + static_cast<long long>(n0) * ES + cn_c * 16;
+        const bool nc_full = w_nc && (p.BN % RS == 0) && (n0 + p.BN <= p.N);
+        const bool cn_full = !w_nc && cn_shape_ok && (static_cast<long long>(n0) * ES + cpr * 16 <= row_bytes_w);
+        const bool tile_full = a_full && (nc_full || cn_full);
+        for (int kt = 0; kt < nk; ++kt, ++g) {
+          const int slot = g % stages, use = g / stages;
+          if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
+          if (!alive) break;
+          if (tid == 0 && g < 48) EGS_MARK(32 + g);
+          const uint32_t base = tiles0 + slot * stage_bytes;
+          const int k0 = kt * KE;
+          const long long koff = static_cast<long long>(k0) * ES;
+          if (tile_full && k0 + KE <= p.C) {
+            // interior stage of a full tile: no predicates, immediate destination offsets
+            const uint32_t da = base + rc_dst0;
+#pragma unroll
+            for (int i = 0; i < kTileM / RS; ++i) cp_async16_full(da + i * (RS * 128u), a_src[i] + koff);
+            if (w_nc) {
+              const char* src = nc_src0 + koff;
+              const uint32_t db = da + b_off;
+              for (int i = 0; i < nb_iters; ++i, src += nc_stride) cp_async16_full(db + i * (RS * 128u), src);
+            } else {
+              const char* src = cn_src0 + static_cast<long long>(k0) * row_bytes_w;
+              const uint32_t db = base + b_off + cn_dst0;
+              const uint32_t dstep = static_cast<uint32_t>(cn_rstep) * 128u;
+              for (int r = cn_r0, i = 0; r < KE; r += cn_rstep, ++i, src += cn_stride) cp_async16_full(db + i * dstep, src);
+            }
+          } else {
+            const bool kvalid = koff + cc * 16 < row_bytes_a;
+#pragma unroll
+            for (int i = 0; i < kTileM / RS; ++i) {
+              const bool v = kvalid && ((a_mask >> i) & 1u);
+              cp_async16(base + rc_dst0 + i * (RS * 128u), v ? a_src[i] + koff : A, v ? 16u : 0u);
+            }
+            if (w_nc) {
+              const char* src = nc_src0 + koff;
+              for (int i = 0; i < nb_iters; ++i, src += nc_stride) {
+                if (r0 + RS * i >= p.BN) break;
+                const bool v = kvalid && ((nc_mask >> i) & 1u);
+                cp_async16(base + b_off + rc_dst0 + i * (RS * 128u), v ? src : W, v ? 16u : 0u);
+              }
+            } else {
+              const long long noff0 = static_cast<long long>(n0) * ES;
+              for (int idx = tid; idx < KE * cpr; idx += PT) {
+                const int r = idx / cpr, c = idx - r * cpr;
+                const long long noff = noff0 + c * 16;
+                const bool v = (k0 + r) < p.C && noff < row_bytes_w;
+                const char* src = W + (static_cast<long long>(blk.e) * p.C + k0 + r) * row_bytes_w + noff;
+                cp_async16(tile_addr<kMn32>(base + b_off, KE * 128u, r, c), v ? src : W, v ? 16u : 0u);
+              }
+            }
+          }
+          cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
+          if (tid == 0 && g < 48) EGS_MARK(80 + g);
+        }
+      }
+    }
+    cp_async_wait_all();
+  } else if (warp < kPersistProducerWarps + kPersistEpilogueWarps) {
+    // =========================== epilogue ===========================
+    const int ew = warp - kPersistProducerWarps;
+    constexpr int kColGroups = kPersistEpilogueWarps / 4;
+    const int lg = ew & 3, half = ew >> 2;               // TMEM lane group of this warp, which share of the column blocks
+    const uint32_t tile = xpose0 + static_cast<uint32_t>(ew) * 4096u;
+    T* out = static_cast<T*>(p.Out);
+    float* acc_rows = (ES == 2) ? p.acc : reinterpret_cast<float*>(p.Out);   // S: float32 rows being added to
+    const bool direct16 = SCATTER && ES == 2 && p.plan != nullptr && *p.plan == 0;
+    bool alive = true;
+    int t = 0;                                           // tiles finished so far by this CTA
+    for (int rb = blockIdx.x; rb < row_blocks && alive; rb += gridDim.x) {
+      const RowBlock blk = row_block_of(p, rb, m_tiles);
+      int src_row, my_ro;                                // destination row of tile row lg*32 + lane
+      lookup_rows<SCATTER>(p, blk.e, blk.m0 + lg * 32 + lane, src_row, my_ro, half == 0);
+      for (int nt = 0; nt < n_tiles && alive; ++nt, ++t) {
+        const int n0 = nt * p.BN;
+        const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);
+        const int buf = t & 1;
+        alive = mbar_wait_warp(smem_u32(&hdr->acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, lane);
+        if (!alive) break;
+        tc_fence_after();
+        if (ew == 0 && lane == 0 && t < 12) EGS_MARK(176 + 2 * t);
+        const int nblk = (bn + 31) >> 5;
+        for (int c = half; c < nblk; c += kColGroups) {
+          const int col0 = n0 + c * 32;
+          warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + buf * acc_cols + static_cast<uint32_t>(c * 32), tile, lane,
+                          true, [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                            const int ro = __shfl_sync(0xffffffffu, my_ro, row);
+                            const int col = col0 + cj;
+                            if (ro >= 0 && col < p.N) {
+                              const long long off = static_cast<long long>(ro) * p.N + col;
+                              if (SCATTER) {
+                                if (direct16) red4(out + off, x0, x1, x2, x3);
+                                else red4(acc_rows + off, x0, x1, x2, x3);
+                              } else {
+                                store4(out + off, x0, x1, x2, x3);
+                              }
+                            }
+                          });
+        }
+        // hand the accumulator buffer back to the MMA lane
+        if (ew == 0 && lane == 0 && t < 12) EGS_MARK(177 + 2 * t);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&hdr->acc_empty[buf]));
+      }
+    }
+  } else {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
+      const uint32_t b_sbo = w_nc ? 1024u : kMnSbo;
+      const uint32_t b_lay = w_nc ? kSwizzle128 : kMnLayout;
+      const uint64_t a_adv = 32u >> 4, b_adv = (w_nc ? 32u : UK * 128u) >> 4;
+      bool ok = true;
+      int g = 0, t = 0;
+      for (int rb = blockIdx.x; rb < row_blocks && ok; rb += gridDim.x) {
+        for (int nt = 0; nt < n_tiles && ok; ++nt, ++t) {
+          const int n0 = nt * p.BN;
+          const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);
+          const uint32_t idesc = make_idesc(Elem<T>::fmt, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(bn));
+          const int buf = t & 1;
+          if (t >= 2) {
+            ok = mbar_wait(smem_u32(&hdr->acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          const uint32_t d = tmem_base + buf * acc_cols;
+          for (int ks = 0; ks < nk; ++ks, ++g) {
+            const int slot = g % stages;
+            ok = mbar_wait(smem_u32(&hdr->full[slot]), (g / stages) & 1, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            if (g < 48) EGS_MARK(128 + g);
+            const uint32_t a_hi = tiles0 + slot * stage_bytes;
+            uint64_t ad = make_smem_desc(a_hi, 16u, 1024u);
+            uint64_t bd = make_smem_desc(a_hi + b_off, b_lbo, b_sbo, b_lay);
+            const int krem = p.C - ks * KE;
+            const int nkq = min(KE / UK, (krem + UK - 1) / UK);
+            for (int kq = 0; kq < nkq; ++kq) {
+              umma<Elem<T>::tf32>(d, ad, bd, idesc, (ks > 0 || kq > 0) ? 1u : 0u);
+              ad += a_adv;
+              bd += b_adv;
+            }
+            umma_commit(smem_u32(&hdr->empty[slot]));
+          }
+          if (ok) umma_commit(smem_u32(&hdr->acc_full[buf]));
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- common exit ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == mma_warp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Operator D.   grid = (ceil(FG/128), ceil(FD/BN), E*splits)
 //   accumulator tile P[f, g]: TMEM lane = f (feature of the gathered rows), column = g
 //   A = gathered token rows of Xsrc, B = slot rows of Ysrc; both consumed MN-major (rows = contraction)
@@ -1203,6 +1541,23 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   const size_t a_bytes = static_cast<size_t>(kTileM) * p.row_tiles * 128;
   const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
   const long long ctas = static_cast<long long>((p.M + kTileM * p.row_tiles - 1) / (kTileM * p.row_tiles)) * n_tiles * p.E;
+  // persistent variant (see its kernel): scatter problems with many tiles, non-strict arithmetic
+  static const int persist_env = getenv("EGS_B200_PERSISTENT") ? env_int("EGS_B200_PERSISTENT") : -1;
+  const long long tiles1 = static_cast<long long>((p.M + kTileM - 1) / kTileM) * n_tiles * p.E;
+  p.persistent = 0;
+  // (measured: it wins for contractions of up to four stages - the scatter of cfg4 and cfg2 - and loses for longer ones)
+  if (!strict && persist_env != 0 && ((scatter && p.C * es <= 512) || persist_env == 2) && tiles1 >= 2 * kSmCount) {
+    const size_t st1 = static_cast<size_t>(kTileM) * 128 + b_bytes;
+    const size_t fixed_p = kPersistHeaderBytes + kPersistMaxEpilogueWarps * 4096;
+    size_t ns = (kSmemMaxPerCta - fixed_p) / st1;
+    if (ns > static_cast<size_t>(kMaxStages)) ns = kMaxStages;
+    if (ns >= 3) {
+      p.persistent = 1;
+      p.row_tiles = 1;
+      p.stages = static_cast<int>(ns);
+      return fixed_p + ns * st1;
+    }
+  }
   p.stages = pick_stages(fixed, stage_bytes, ctas, p.row_tiles == 1);
   return fixed + p.stages * stage_bytes;
 }
@@ -1256,6 +1611,29 @@ static cudaError_t ensure_smem_optin() {
 
 cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtype, int precision, size_t smem_bytes,
                                   cudaStream_t st) {
+  if (p.persistent) {
+    const int row_blocks = p.E * ((p.M + kTileM - 1) / kTileM);
+    dim3 pgrid(row_blocks < kSmCount ? row_blocks : kSmCount);
+    dim3 pblock(scatter ? PersistShape<true>::kThreads : PersistShape<false>::kThreads);
+    cudaError_t perr = cudaSuccess;
+#define EGS_LAUNCH_P(TY)                                                                                     \
+  do {                                                                                                       \
+    if (scatter) {                                                                                           \
+      perr = (ensure_smem_optin<tensor_rowgemm_persistent_kernel<TY, true>>());                              \
+      if (perr == cudaSuccess) tensor_rowgemm_persistent_kernel<TY, true><<<pgrid, pblock, smem_bytes, st>>>(p);  \
+    } else {                                                                                                 \
+      perr = (ensure_smem_optin<tensor_rowgemm_persistent_kernel<TY, false>>());                             \
+      if (perr == cudaSuccess) tensor_rowgemm_persistent_kernel<TY, false><<<pgrid, pblock, smem_bytes, st>>>(p); \
+    }                                                                                                        \
+  } while (0)
+    if (dtype == EGS_F32) EGS_LAUNCH_P(float);
+    else if (dtype == EGS_F16) EGS_LAUNCH_P(__half);
+    else EGS_LAUNCH_P(__nv_bfloat16);
+#undef EGS_LAUNCH_P
+    if (perr != cudaSuccess) return perr;
+    count_launch();
+    return cudaGetLastError();
+  }
   const int rows_per_cta = kTileM * p.row_tiles;
   const int row_tiles = (p.M + rows_per_cta - 1) / rows_per_cta;
   dim3 grid(p.expert_fastest ? p.E : row_tiles, (p.N + p.BN - 1) / p.BN, p.expert_fastest ? row_tiles : p.E);
