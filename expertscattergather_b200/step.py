@@ -25,21 +25,30 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
 
     With ``overlap`` the work that is off the critical chain G -> S -> dY -> dX runs on a side stream: the zero
     fills of Out and dX (float32 tensors; 16-bit outputs are initialised by the scatter's own planning step) and
-    the two weight-gradient kernels, each started as soon as its inputs exist.  ``on_weight_grad`` is called on
-    that side stream right after the gradient has been enqueued.
+    the two weight-gradient kernels, each started as soon as its inputs exist.  With ``on_weight_grad`` (the
+    data-parallel case) everything stays on one stream in an order that puts both weight gradients, and with them
+    the start of their reductions, before the last scatter.
     """
     T = X.shape[1]
+    if on_weight_grad is not None:
+        # data-parallel order: both weight gradients come before the long dX scatter, so that the reductions the
+        # callback starts (dW_s first, then dW_g) run behind the kernels that are still to come
+        Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")
+        Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn")
+        dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")
+        dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")
+        on_weight_grad("Ws", dWs)
+        dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
+        on_weight_grad("Wg", dWg)
+        dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc")
+        return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
     if not overlap:
         Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                 # gather forward
         Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn")           # scatter forward
         dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                # scatter backward: dY
         dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")         # scatter backward: dW_s
-        if on_weight_grad is not None:
-            on_weight_grad("Ws", dWs)
         dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc")           # gather backward: dX
         dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")      # gather backward: dW_g
-        if on_weight_grad is not None:
-            on_weight_grad("Wg", dWg)
         return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
 
     dev = X.device
@@ -64,16 +73,12 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         side.wait_event(fwd_done)                                      # the backward pass starts after the forward
         dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")
         dWs.record_stream(main)
-        if on_weight_grad is not None:
-            on_weight_grad("Ws", dWs)
     dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                    # scatter backward: dY
     dy_ready = main.record_event()
     with torch.cuda.stream(side):                                      # gather backward: dW_g, next to dX
         side.wait_event(dy_ready)
         dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
         dWg.record_stream(main)
-        if on_weight_grad is not None:
-            on_weight_grad("Wg", dWg)
     dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc", out=dX)       # gather backward: dX
     main.wait_stream(side)                                             # join
     return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}

@@ -278,3 +278,46 @@ def test_no_gathered_intermediate_is_allocated(cuda_device):
     gathered_block = w.B * w.E * w.K * w.I * 2
     assert peak <= outputs + scratch + (1 << 20), (peak, outputs, scratch)
     assert gathered_block > (1 << 22)     # the block the reference's torch path materialises would be visible
+
+
+# ---------------------------------------------------------------------------------------------------------
+# ragged shapes that reach the large-problem kernel variants (256-row CTA tiles for G, the persistent
+# warp-specialised scatter, direct 16-bit adds) - compared with the generic kernels and the CPU checker
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,precision", [(torch.bfloat16, "strict"), (torch.float32, "tf32")])
+def test_large_variants_on_ragged_shapes(cuda_device, dtype, precision):
+    # M = B*K = 500 rows per expert (not a multiple of 128 or 256), J = 72 (two contraction stages for S, the second
+    # partial), I = 1320 (six 256-wide output tiles for S, the last 40 wide; 21 or 42 contraction stages for G)
+    w = Workload("ragged-large", 5, 300, 80, 100, 1320, 72, dtype, "replace", 808)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    ins["Ind"][2, 7, 5] = 300          # out of range: skipped and reported
+    ins["Ind"][4, 79, 99] = -3
+    ref_ind = ins["Ind"].clamp(0, 299)
+    d = to_dev(ins, cuda_device)
+    res = {}
+    for path in ("generic", "tensor"):
+        ops.reset_status()
+        Y = ops.gather_gemm(d["X"], d["Wg"], d["Ind"], path=path, precision=precision)
+        Out = ops.gemm_scatter(Y, d["Ws"], d["Ind"], w.T, path=path, precision=precision)
+        dY = ops.gather_gemm(d["G"], d["Ws"], d["Ind"], w_layout="nc", path=path, precision=precision)
+        dX = ops.gemm_scatter(dY, d["Wg"], d["Ind"], w.T, w_layout="nc", path=path, precision=precision)
+        dWg = ops.dweight(d["X"], dY, d["Ind"], path=path, precision=precision)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="outside"):
+            ops.check_status()
+        res[path] = {"Y": Y.cpu(), "Out": Out.cpu(), "dY": dY.cpu(), "dX": dX.cpu(), "dWg": dWg.cpu()}
+    # integer-valued inputs: Y and dY are exact in every dtype, so both families must agree bit for bit there
+    for k in ("Y", "dY"):
+        assert torch.equal(res["generic"][k], res["tensor"][k]), k
+    # and with the checker on the rows whose index is valid (masked slots give zero rows / add nothing)
+    Yref = orc.np_gather(ins["X"], ins["Wg"], ref_ind)
+    bad = torch.zeros_like(ins["Ind"], dtype=torch.bool)
+    bad[2, 7, 5] = True
+    bad[4, 79, 99] = True
+    Yref[bad.numpy()] = 0
+    assert np.array_equal(res["tensor"]["Y"].double().numpy(), Yref)
+    tol = tol_for(dtype, precision)
+    for k in ("Out", "dX", "dWg"):
+        assert orc.rel_err(res["tensor"][k], res["generic"][k]) <= tol, (k, orc.rel_err(res["tensor"][k], res["generic"][k]))
+    Outref = orc.np_scatter(torch.from_numpy(Yref), ins["Ws"], ref_ind, w.T)
+    assert orc.rel_err(res["tensor"]["Out"], Outref) <= tol
