@@ -24,6 +24,7 @@ STATUS_INDEX_OUT_OF_RANGE, STATUS_PIPELINE_TIMEOUT, STATUS_INTERNAL = 1, 2, 4
 EXPORTS = (
     "egs_version", "egs_status_string", "egs_last_cuda_error", "egs_gather_gemm", "egs_gemm_scatter",
     "egs_dweight", "egs_dweight_static_scratch", "egs_static_scratch_max_elements", "egs_dw_workspace_bytes", "egs_scatter_workspace_bytes", "egs_tensor_path_eligible", "egs_fill_zero", "egs_launch_count",
+    "egs_gather_scatter_pair", "egs_fused_pair_eligible",
 )
 
 
@@ -63,6 +64,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_fill_zero.argtypes = [vp, sz, vp]
     lib.egs_launch_count.restype = i64
     lib.egs_launch_count.argtypes = []
+    lib.egs_gather_scatter_pair.restype = i
+    lib.egs_gather_scatter_pair.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i, i, i, i, i, vp, vp]
+    lib.egs_fused_pair_eligible.restype = i
+    lib.egs_fused_pair_eligible.argtypes = [i64, i64, i64, i, i, i]
 
 
 def library_path() -> str:

@@ -187,6 +187,48 @@ int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, c
                      workspace_bytes, status_word, cuda_stream);
 }
 
+int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision) {
+  if (dtype != EGS_F32 || C1 > (1 << 24) || N1 > (1 << 24) || N2 > (1 << 24) || C1 < 0 || N1 < 0 || N2 < 0) return 0;
+  if (!device_is_sm100()) return 0;
+  FusedParams p{};
+  p.C1 = static_cast<int>(C1); p.N1 = static_cast<int>(N1); p.N2 = static_cast<int>(N2); p.w_layout = w_layout;
+  return configure_tensor_fused_pair(p, precision) != 0 ? 1 : 0;
+}
+
+int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, const void* Ind, void* Mid, void* Dst,
+                            int64_t B, int64_t T, int64_t E, int64_t K, int64_t C1, int64_t N1, int64_t N2, int w_layout,
+                            int zero_output, int dtype, int index_dtype, int precision, int32_t* status_word,
+                            void* cuda_stream) {
+  egs_dims d1{B, T, E, K, C1, N1}, d2{B, T, E, K, N1, N2};
+  if (int rc = check_dims(&d1)) return rc;
+  if (int rc = check_dims(&d2)) return rc;
+  if (!valid_dtype(dtype) || !valid_index(index_dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
+      (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32))
+    return EGS_ERR_INVALID_ARGUMENT;
+  if (!egs_fused_pair_eligible(C1, N1, N2, w_layout, dtype, precision)) return EGS_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  const size_t dst_bytes = static_cast<size_t>(B) * T * N2 * sizeof(float);
+  if (dst_bytes > 0 && !Dst) return EGS_ERR_INVALID_ARGUMENT;
+  if (zero_output && dst_bytes > 0) {
+    cudaError_t err = launch_fill_zero(Dst, dst_bytes, st);
+    if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+  }
+  if (B * E * K == 0) return EGS_OK;
+  if (!Src || !W1 || !W2 || !Ind || !Mid || !Dst) return EGS_ERR_INVALID_ARGUMENT;
+  if (!aligned16(Src) || !aligned16(W1) || !aligned16(W2) || !aligned16(Mid) || !aligned16(Dst)) return EGS_ERR_UNSUPPORTED;
+  FusedParams p{};
+  p.Src = Src; p.W1 = W1; p.W2 = W2; p.Ind = Ind; p.Mid = Mid; p.Dst = static_cast<float*>(Dst); p.status = status_word;
+  p.B = static_cast<int>(B); p.T = static_cast<int>(T); p.E = static_cast<int>(E); p.K = static_cast<int>(K);
+  p.C1 = static_cast<int>(C1); p.N1 = static_cast<int>(N1); p.N2 = static_cast<int>(N2);
+  p.M = static_cast<int>(B * K);
+  p.w_layout = w_layout; p.index_dtype = index_dtype;
+  const size_t smem = configure_tensor_fused_pair(p, precision);
+  if (smem == 0) return EGS_ERR_UNSUPPORTED;
+  cudaError_t err = launch_tensor_fused_pair(p, precision, smem, st);
+  if (err != cudaSuccess) return fail_cuda(err, "gather_scatter_pair launch");
+  return EGS_OK;
+}
+
 size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype) {
   if (dtype == EGS_F32 || B <= 0 || T <= 0 || N <= 0) return 0;
   const size_t counter_bytes = (static_cast<size_t>(B) * T * sizeof(int) + 255) & ~static_cast<size_t>(255);

@@ -57,6 +57,7 @@ struct RowGemmParams {
   int expert_fastest; // tensor path: grid order (1: experts vary fastest, row tiles slowest)
   int row_tiles;      // tensor path: 128-row accumulator tiles per CTA (1 or 2)
   int persistent;     // tensor path: 1 = persistent warp-specialised variant
+  int bulk_epilogue;  // persistent scatter: rows staged in shared memory and added with bulk asynchronous reductions
 };
 
 struct DWeightParams {
@@ -73,6 +74,25 @@ struct DWeightParams {
   int splits;         // number of row ranges the contraction is split into
   int rows_per_split; // multiple of the stage depth
   int BN;             // tensor path: tile width over FD
+  int stages;
+  int row_tiles;      // tensor path: 128-feature accumulator tiles per CTA over FG (1 or 2)
+};
+
+// Fused pair G -> S on float32 tensors (tensor path only):  Mid = gather(Src) x W1[e] is stored as slot rows AND fed,
+// from shared memory, into  Dst[token rows] += Mid x W2[e].
+struct FusedParams {
+  const void* Src;     // token rows [B*T, C1]
+  const void* W1;      // [E, C1, N1] (EGS_W_CN) or [E, N1, C1] (EGS_W_NC)
+  const void* W2;      // [E, N1, N2] (EGS_W_CN) or [E, N2, N1] (EGS_W_NC)
+  const void* Ind;     // [B, E, K]
+  void* Mid;           // slot rows [B*E*K, N1], overwritten
+  float* Dst;          // token rows [B*T, N2], added to
+  int32_t* status;
+  int B, T, E, K, C1, N1, N2;
+  int M;               // B*K
+  int w_layout;        // of both weights
+  int index_dtype;
+  int BN1, BN2;        // MMA widths (multiples of 16)
   int stages;
 };
 
@@ -99,6 +119,10 @@ cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtyp
                                   size_t smem_bytes, cudaStream_t st);
 cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precision, size_t smem_bytes,
                                   cudaStream_t st);
+
+// Fused pair: `configure` returns 0 when the shape does not fit the kernel (the caller then runs G and S).
+size_t configure_tensor_fused_pair(FusedParams& p, int precision);
+cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t smem_bytes, cudaStream_t st);
 
 void count_launch(int n = 1);
 

@@ -242,6 +242,29 @@ template <> struct Elem<float> { static constexpr uint32_t fmt = 2; static const
 template <> struct Elem<__half> { static constexpr uint32_t fmt = 0; static constexpr bool tf32 = false; };
 template <> struct Elem<__nv_bfloat16> { static constexpr uint32_t fmt = 1; static constexpr bool tf32 = false; };
 
+// Optional phase trace (compile with -DEGS_TRACE): CTA (0,0,0) records globaltimer stamps of its phases.
+#ifdef EGS_TRACE
+__device__ unsigned long long g_trace[256];
+__device__ __forceinline__ void trace_mark(int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_trace[slot] = t;
+  }
+}
+#define EGS_MARK(slot) trace_mark(slot)
+// cycle accounting of one role of CTA 0:  EGS_TIC(); ...wait...; EGS_TOC(slot) adds the elapsed clock64 ticks
+#define EGS_TIC() const long long egs_tic_ = clock64()
+#define EGS_TOC(slot)                                                          \
+  do {                                                                         \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_trace[slot] += static_cast<unsigned long long>(clock64() - egs_tic_); \
+  } while (0)
+#else
+#define EGS_MARK(slot)
+#define EGS_TIC()
+#define EGS_TOC(slot)
+#endif
+
 // ---- epilogue helpers ----
 __device__ __forceinline__ uint32_t pack2(__half*, uint32_t a, uint32_t b) {
   const __half2 h = __floats2half2_rn(__uint_as_float(a), __uint_as_float(b));
@@ -259,6 +282,10 @@ __device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, uint32_t a, uint32_t b
 template <class Emit>
 __device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, int lane, bool have_acc, Emit&& emit) {
   uint32_t v[32];
+#ifdef EGS_TRACE
+  const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && ((threadIdx.x >> 5) & 7) == 0);
+  const long long c0 = clock64();
+#endif
   if (have_acc) {
     tmem_ld32(taddr, v);
     tmem_ld_wait();
@@ -266,6 +293,9 @@ __device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, i
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = 0u;
   }
+#ifdef EGS_TRACE
+  const long long c1 = clock64();
+#endif
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + lane * 128u + (static_cast<uint32_t>(j ^ (lane & 7)) << 4)),
@@ -283,8 +313,20 @@ __device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, i
                  : "memory");
   }
   __syncwarp();                         // the tile may be overwritten from here on
+#ifdef EGS_TRACE
+  const long long c2 = clock64();
+#endif
 #pragma unroll
   for (int it = 0; it < 8; ++it) emit(it * 4 + (lane >> 3), j * 4, x[it][0], x[it][1], x[it][2], x[it][3]);
+#ifdef EGS_TRACE
+  if (tr) {
+    const long long c3 = clock64();
+    g_trace[232] += static_cast<unsigned long long>(c1 - c0);   // tcgen05.ld + wait
+    g_trace[233] += static_cast<unsigned long long>(c2 - c1);   // transpose through shared memory
+    g_trace[234] += static_cast<unsigned long long>(c3 - c2);   // emit (stores / reds)
+    g_trace[235] += 1ull;
+  }
+#endif
 }
 // Same transpose for a 32-row x 64-column block (8 KB tile): every lane ends up with 8 consecutive columns of
 // one row, so 8 lanes cover 64 columns - 128 contiguous bytes of a 16-bit row per instruction.
@@ -329,6 +371,24 @@ __device__ __forceinline__ void red8(__half* dst, const uint32_t (&x)[8]) {
                : "memory");
 }
 __device__ __forceinline__ void red8(float*, const uint32_t (&)[8]) {}   // never taken: direct adds are 16-bit only
+// Bulk asynchronous reduction: adds `bytes` (multiple of 16) of elements staged in shared memory to global memory.
+// The copy engine reads the shared memory after the instruction has issued: the staging buffer may be rewritten
+// only after bulk_wait_read, and the issuing thread's own writes need fence.proxy.async before the instruction.
+__device__ __forceinline__ void bulk_reduce_add(__nv_bfloat16* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_reduce_add(__half* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+constexpr uint32_t kBulkRowPitch = 144;                  // 128 staged bytes per row + 16: conflict-free 16-byte stores
+constexpr uint32_t kBulkBufBytes = 32 * kBulkRowPitch;   // one 32-row staging buffer
 __device__ __forceinline__ void red4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
   asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(__uint_as_float(x0)), "f"(__uint_as_float(x1)),
                "f"(__uint_as_float(x2)), "f"(__uint_as_float(x3))
@@ -358,20 +418,7 @@ __device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
 // hand out a differently aligned base, the CTA refuses to work and reports EGS_STATUS_INTERNAL.
 __device__ __forceinline__ bool smem_misaligned(const void* raw) { return (smem_u32(raw) & 1023u) != 0u; }
 
-// Optional phase trace (compile with -DEGS_TRACE): CTA (0,0,0) records globaltimer stamps of its phases.
-#ifdef EGS_TRACE
-__device__ unsigned long long g_trace[256];
-__device__ __forceinline__ void trace_mark(int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[slot] = t;
-  }
-}
-#define EGS_MARK(slot) trace_mark(slot)
-#else
-#define EGS_MARK(slot)
-#endif
+
 
 // ------------------------------------------------------------------------------------------------
 // Pipeline pieces shared by the two kernels
@@ -448,7 +495,11 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
   if (!STRICT) {
     for (int kt = 0; kt < nk; ++kt) {
       const int slot = kt % stages, use = kt / stages;
-      if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
+      {
+        EGS_TIC();
+        if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
+        if (threadIdx.x == 0) EGS_TOC(248);
+      }
       if (!alive) break;
       if (threadIdx.x == 0 && kt < 64) EGS_MARK(32 + kt);
       issue(kt, pp.tiles0 + slot * pp.stage_bytes);
@@ -513,9 +564,16 @@ template <class Mma>
 __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
   SmemHeader* hdr = pp.hdr;
   bool ok = true;
+#ifdef EGS_TRACE
+  const long long lane_t0 = clock64();
+#endif
   for (int ks = 0; ks < pp.nk; ++ks) {
     const int slot = ks % pp.stages;
-    ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / pp.stages) & 1, pp.abort_flag, pp.status);
+    {
+      EGS_TIC();
+      ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / pp.stages) & 1, pp.abort_flag, pp.status);
+      EGS_TOC(247);
+    }
     if (!ok) break;
     tc_fence_after();
     if (ks == 0) EGS_MARK(6);
@@ -525,6 +583,12 @@ __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
     umma_commit(smem_u32(&hdr->empty[slot]));
   }
   if (ok && pp.nk > 0) umma_commit(smem_u32(&hdr->done));
+#ifdef EGS_TRACE
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    g_trace[249] += static_cast<unsigned long long>(clock64() - lane_t0);
+    g_trace[250] += static_cast<unsigned long long>(pp.nk);
+  }
+#endif
   EGS_MARK(7);
 }
 
@@ -677,12 +741,13 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
     // range): no predicates, destination offsets are immediates, about two instructions per copy.
     const bool a_full = (a_mask == (1u << (kRows / 32)) - 1u);
     const bool nc_full = w_nc && (p.BN % 32 == 0) && (n0 + p.BN <= p.N);
-    const bool cn_full = !w_nc && cn_fast && (KE % cn_rstep == 0) && (cn_rstep % 8 == 0 || kMn32) &&
+    const bool cn_full = !w_nc && cn_fast && (KE % cn_rstep == 0) &&
                          (static_cast<long long>(n0) * ES + cpr * 16 <= row_bytes_w);
     const bool tile_full = a_full && (nc_full || cn_full);
-    const uint32_t cn_dst0 = cn_dst_seg + static_cast<uint32_t>(cn_r0) * 128u +
-                             (kMn32 ? ((static_cast<uint32_t>(((cn_c & 7) >> 1) ^ (cn_r0 & 3)) << 5) + (static_cast<uint32_t>(cn_c & 1) << 4))
-                                    : (static_cast<uint32_t>((cn_c & 7) ^ (cn_r0 & 7)) << 4));
+    auto cn_swz = [&](int r) -> uint32_t {
+      return kMn32 ? ((static_cast<uint32_t>(((cn_c & 7) >> 1) ^ (r & 3)) << 5) + (static_cast<uint32_t>(cn_c & 1) << 4))
+                   : (static_cast<uint32_t>((cn_c & 7) ^ (r & 7)) << 4);
+    };
     auto issue_full = [&](int kt, uint32_t stage_base) {
       const long long koff = static_cast<long long>(kt) * 128;
       const uint32_t da = stage_base + rc_dst0;
@@ -694,9 +759,9 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
         for (int i = 0; i < nb_iters; ++i, src += nc_stride) cp_async16_full(db + i * 4096u, src);
       } else {
         const char* src = cn_src0 + static_cast<long long>(kt * KE) * row_bytes_w;
-        const uint32_t db = stage_base + b_off + cn_dst0;
-        const uint32_t dstep = static_cast<uint32_t>(cn_rstep) * 128u;
-        for (int r = cn_r0, i = 0; r < KE; r += cn_rstep, ++i, src += cn_stride) cp_async16_full(db + i * dstep, src);
+        const uint32_t db = stage_base + b_off + cn_dst_seg;
+        for (int r = cn_r0; r < KE; r += cn_rstep, src += cn_stride)
+          cp_async16_full(db + static_cast<uint32_t>(r) * 128u + cn_swz(r), src);
       }
     };
     // strict float32: when this thread's chunk list has the fixed 4 + 4 shape the in-place hi/lo split reads all
@@ -765,7 +830,45 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
       // direct 16-bit adds go out in 64-column blocks (128-byte row segments) when the ring has room for the
       // eight 8 KB transpose tiles and the tile width is a multiple of 64
       const bool wide16 = direct16 && (bn % 64 == 0) && (pp.stages * pp.stage_bytes >= 8u * 8192u);
-      if (wide16) {
+      // direct 16-bit adds as bulk reductions: every lane stages 128 bytes (64 columns) of its own row in the idle
+      // ring and hands them to the copy engine (see the persistent variant)
+      static_assert(2u * kBulkBufBytes <= 16384u, "two staging buffers per warp");
+      const bool bulk16 = direct16 && p.bulk_epilogue && (pp.stages * pp.stage_bytes >= 8u * 2u * kBulkBufBytes);
+      if (bulk16) {
+        if constexpr (ES == 2 && SCATTER) {
+          const uint32_t my_stage = pp.tiles0 + static_cast<uint32_t>(warp) * (2u * kBulkBufBytes) + static_cast<uint32_t>(lane) * kBulkRowPitch;
+          int q = 0;
+          for (int mt = 0; mt < MT; ++mt) {
+            const int ro = hdr->row_o[mt * kTileM + lg * 32 + lane];
+            const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + mt * acc_cols;
+            for (int c = half; c * 64 < bn; c += 2, ++q) {
+              const uint32_t srow = my_stage + static_cast<uint32_t>(q & 1) * kBulkBufBytes;
+              if (q >= 2) bulk_wait_read_1();
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (c * 64 + h * 32 < bn) {
+                  uint32_t v[32];
+                  tmem_ld32(acc0 + static_cast<uint32_t>(c * 64 + h * 32), v);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(srow + h * 64u + j * 16u),
+                                 "r"(pack2(out, v[8 * j], v[8 * j + 1])), "r"(pack2(out, v[8 * j + 2], v[8 * j + 3])),
+                                 "r"(pack2(out, v[8 * j + 4], v[8 * j + 5])), "r"(pack2(out, v[8 * j + 6], v[8 * j + 7]))
+                                 : "memory");
+                }
+              }
+              fence_proxy_async_smem();
+              const int col0 = n0 + c * 64;
+              const int ncols = min(64, p.N - col0);
+              if (ro >= 0 && ncols > 0)
+                bulk_reduce_add(out + static_cast<long long>(ro) * p.N + col0, srow, static_cast<uint32_t>(ncols) * 2u);
+              bulk_commit();
+            }
+          }
+          bulk_wait_all();                               // shared memory must outlive the copy engine's reads
+        }
+      } else if (wide16) {
         const uint32_t tile8 = pp.tiles0 + static_cast<uint32_t>(warp) * 8192u;
         for (int mt = 0; mt < MT; ++mt) {
           for (int c = half; c < (bn >> 6); c += 2) {
@@ -812,17 +915,16 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
       const uint64_t a_adv = 32u >> 4, b_adv = b_step >> 4;
       run_mma_lane(pp, [&](int ks, uint32_t a_hi) {
         const uint32_t b_hi = a_hi + b_off;
-        const int krem = p.C - ks * KE;
-        const int nkq = min(KE / UK, (krem + UK - 1) / UK);
+        const int kq0 = 0, kq1 = min(KE / UK, (p.C - ks * KE + UK - 1) / UK);
         uint64_t ad[MT], adl[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          ad[mt] = make_smem_desc(a_hi + mt * (kTileM * 128u), 16u, 1024u);
-          adl[mt] = STRICT ? make_smem_desc(a_hi + mt * (kTileM * 128u) + a_lo_off, 16u, 1024u) : 0ull;
+          ad[mt] = make_smem_desc(a_hi + mt * (kTileM * 128u), 16u, 1024u) + kq0 * a_adv;
+          adl[mt] = STRICT ? make_smem_desc(a_hi + mt * (kTileM * 128u) + a_lo_off, 16u, 1024u) + kq0 * a_adv : 0ull;
         }
-        uint64_t bd = make_smem_desc(b_hi, b_lbo, b_sbo, b_lay);
-        uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off, b_lbo, b_sbo, b_lay) : 0ull;
-        for (int kq = 0; kq < nkq; ++kq) {
+        uint64_t bd = make_smem_desc(b_hi, b_lbo, b_sbo, b_lay) + kq0 * b_adv;
+        uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off, b_lbo, b_sbo, b_lay) + kq0 * b_adv : 0ull;
+        for (int kq = kq0; kq < kq1; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
@@ -932,7 +1034,9 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
   PersistHeader* hdr = reinterpret_cast<PersistHeader*>(smem_raw);
   const uint32_t smem0 = smem_u32(smem_raw);
   const uint32_t xpose0 = smem0 + kPersistHeaderBytes;                             // 8 transpose tiles of 4 KB
-  const uint32_t tiles0 = xpose0 + kPersistMaxEpilogueWarps * 4096u;               // stage ring
+  // per epilogue warp: a 4 KB transpose tile, or the two staging buffers of the bulk adds (the tile fits in them)
+  const uint32_t xpose_tile = p.bulk_epilogue ? 2u * kBulkBufBytes : 4096u;
+  const uint32_t tiles0 = xpose0 + ((kPersistMaxEpilogueWarps * xpose_tile + 1023u) & ~1023u);   // stage ring
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) EGS_MARK(0);
@@ -1029,7 +1133,11 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
         const bool tile_full = a_full && (nc_full || cn_full);
         for (int kt = 0; kt < nk; ++kt, ++g) {
           const int slot = g % stages, use = g / stages;
-          if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
+          {
+            EGS_TIC();
+            if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
+            if (tid == 0) EGS_TOC(244);
+          }
           if (!alive) break;
           if (tid == 0 && g < 48) EGS_MARK(32 + g);
           const uint32_t base = tiles0 + slot * stage_bytes;
@@ -1086,10 +1194,16 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
     const int ew = warp - kPersistProducerWarps;
     constexpr int kColGroups = kPersistEpilogueWarps / 4;
     const int lg = ew & 3, half = ew >> 2;               // TMEM lane group of this warp, which share of the column blocks
-    const uint32_t tile = xpose0 + static_cast<uint32_t>(ew) * 4096u;
+    const uint32_t tile = xpose0 + static_cast<uint32_t>(ew) * xpose_tile;
     T* out = static_cast<T*>(p.Out);
     float* acc_rows = (ES == 2) ? p.acc : reinterpret_cast<float*>(p.Out);   // S: float32 rows being added to
     const bool direct16 = SCATTER && ES == 2 && p.plan != nullptr && *p.plan == 0;
+    // bulk adds (direct 16-bit scatter): every lane stages 128 bytes of its own row and hands them to the copy
+    // engine - no transpose, no shuffles, and the warp does not wait on the load/store unit.  (For float32 rows
+    // the same scheme needs twice the operations per column and measured slower than the transposed reds.)
+    const bool bulk = direct16 && p.bulk_epilogue;
+    const uint32_t my_stage = tile + static_cast<uint32_t>(lane) * kBulkRowPitch;
+    int q = 0;                                           // bulk groups committed so far by this thread
     bool alive = true;
     int t = 0;                                           // tiles finished so far by this CTA
     for (int rb = blockIdx.x; rb < row_blocks && alive; rb += gridDim.x) {
@@ -1100,11 +1214,46 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
         const int n0 = nt * p.BN;
         const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);
         const int buf = t & 1;
-        alive = mbar_wait_warp(smem_u32(&hdr->acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, lane);
+        {
+          EGS_TIC();
+          alive = mbar_wait_warp(smem_u32(&hdr->acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, lane);
+          if (ew == 0 && lane == 0) EGS_TOC(242);
+        }
         if (!alive) break;
         tc_fence_after();
         if (ew == 0 && lane == 0 && t < 12) EGS_MARK(176 + 2 * t);
+        EGS_TIC();
         const int nblk = (bn + 31) >> 5;
+        if (bulk) {
+          const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + buf * acc_cols;
+          if constexpr (ES == 2) {
+            // 64 columns = 128 bytes of a 16-bit row per block
+            for (int c = half; c * 64 < bn; c += kColGroups, ++q) {
+              const uint32_t srow = my_stage + static_cast<uint32_t>(q & 1) * kBulkBufBytes;
+              if (q >= 2) bulk_wait_read_1();            // the group that used this buffer two blocks ago has been read
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (c * 64 + h * 32 < bn) {
+                  uint32_t v[32];
+                  tmem_ld32(acc0 + static_cast<uint32_t>(c * 64 + h * 32), v);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(srow + h * 64u + j * 16u),
+                                 "r"(pack2(out, v[8 * j], v[8 * j + 1])), "r"(pack2(out, v[8 * j + 2], v[8 * j + 3])),
+                                 "r"(pack2(out, v[8 * j + 4], v[8 * j + 5])), "r"(pack2(out, v[8 * j + 6], v[8 * j + 7]))
+                                 : "memory");
+                }
+              }
+              fence_proxy_async_smem();
+              const int col0 = n0 + c * 64;
+              const int ncols = min(64, p.N - col0);
+              if (my_ro >= 0 && ncols > 0)
+                bulk_reduce_add(out + static_cast<long long>(my_ro) * p.N + col0, srow, static_cast<uint32_t>(ncols) * 2u);
+              bulk_commit();
+            }
+          }
+        } else
         for (int c = half; c < nblk; c += kColGroups) {
           const int col0 = n0 + c * 32;
           warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + buf * acc_cols + static_cast<uint32_t>(c * 32), tile, lane,
@@ -1124,11 +1273,13 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
         }
         // hand the accumulator buffer back to the MMA lane
         if (ew == 0 && lane == 0 && t < 12) EGS_MARK(177 + 2 * t);
+        if (ew == 0 && lane == 0) EGS_TOC(243);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->acc_empty[buf]));
       }
     }
+    if (bulk) bulk_wait_all();                           // shared memory must outlive the copy engine's reads
   } else {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
@@ -1138,6 +1289,9 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
       const uint64_t a_adv = 32u >> 4, b_adv = (w_nc ? 32u : UK * 128u) >> 4;
       bool ok = true;
       int g = 0, t = 0;
+#ifdef EGS_TRACE
+      const long long lane_t0 = clock64();
+#endif
       for (int rb = blockIdx.x; rb < row_blocks && ok; rb += gridDim.x) {
         for (int nt = 0; nt < n_tiles && ok; ++nt, ++t) {
           const int n0 = nt * p.BN;
@@ -1145,14 +1299,18 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
           const uint32_t idesc = make_idesc(Elem<T>::fmt, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(bn));
           const int buf = t & 1;
           if (t >= 2) {
+            EGS_TIC();
             ok = mbar_wait(smem_u32(&hdr->acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status);
+            EGS_TOC(241);
             if (!ok) break;
             tc_fence_after();
           }
           const uint32_t d = tmem_base + buf * acc_cols;
           for (int ks = 0; ks < nk; ++ks, ++g) {
             const int slot = g % stages;
+            EGS_TIC();
             ok = mbar_wait(smem_u32(&hdr->full[slot]), (g / stages) & 1, abort_flag, p.status);
+            EGS_TOC(240);
             if (!ok) break;
             tc_fence_after();
             if (g < 48) EGS_MARK(128 + g);
@@ -1171,6 +1329,12 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
           if (ok) umma_commit(smem_u32(&hdr->acc_full[buf]));
         }
       }
+#ifdef EGS_TRACE
+      if (blockIdx.x == 0) {
+        g_trace[245] += static_cast<unsigned long long>(clock64() - lane_t0);
+        g_trace[246] += static_cast<unsigned long long>(t);
+      }
+#endif
     }
     __syncwarp();
   }
@@ -1190,13 +1354,16 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
 //   A = gathered token rows of Xsrc, B = slot rows of Ysrc; both consumed MN-major (rows = contraction)
 //   The token row of every contraction row this CTA owns is looked up once into a shared-memory table.
 //   splits == 1: the tile is stored in the output dtype; splits > 1: red.global.add.f32 into p.acc
+//   MT = 128-feature accumulator tiles per CTA over FG (1 or 2).  With MT = 2 both accumulators are fed from
+//   the same B tile: a third fewer bytes loaded per flop, which is what bounds this kernel once the contraction
+//   is long (the loads of two 128 x 256 CTAs per SM top out well below the tensor rate).
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool STRICT>
-__global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightParams p) {
+template <typename T, bool STRICT, int MT>
+__global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_dweight_kernel(DWeightParams p) {
   constexpr int ES = sizeof(T);
   constexpr int KR = 128 / ES;          // contraction rows per stage (4 MMAs of UK rows)
   constexpr int UK = 32 / ES;           // contraction rows per tcgen05.mma
-  constexpr int NSEG_A = ES;            // 128 features * ES bytes / 128
+  constexpr int NSEG_A = ES * MT;       // 128*MT features * ES bytes / 128
   constexpr int CPR_A = NSEG_A * 8;     // 16-byte chunks per A row
   constexpr bool kMn32 = (ES == 4);     // MN-major 32-bit tiles use the 32-byte-granule swizzle
   constexpr uint32_t kMnLayout = kMn32 ? kSwizzle128Base32 : kSwizzle128;
@@ -1211,7 +1378,7 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
   if (tid == 0) EGS_MARK(0);
   const int e = blockIdx.z / p.splits;
   const int split = blockIdx.z - e * p.splits;
-  const int f0 = blockIdx.x * kTileM;
+  const int f0 = blockIdx.x * (kTileM * MT);
   const int g0 = blockIdx.y * p.BN;
   const int bn = min(p.BN, ((p.FD - g0) + 15) & ~15);
   const int m_begin = split * p.rows_per_split;
@@ -1245,7 +1412,8 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
     else if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
     row_tok[i] = tok;
   }
-  const uint32_t tmem_cols = tmem_cols_for(p.BN);
+  const uint32_t acc_cols = tmem_cols_for(p.BN);
+  const uint32_t tmem_cols = acc_cols * MT;
   const uint32_t tmem_base = pipe_setup(pp, STRICT ? kProducerWarps : kProducerThreads, tmem_cols, tid, warp);
   const bool run = (hdr->abort_flag == 0u);
 
@@ -1332,11 +1500,16 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
     auto issue_full = [&](int kt, uint32_t stage_base) {
       const int i0 = kt * KR;
       const uint32_t da = stage_base + a_dst0;
+      // all table reads first: a copy instruction orders the memory accesses around it, so a look-up between
+      // two copies would put its shared-memory latency on every copy
+      constexpr int kIterA = KR / a_rstep;
+      int tok[kIterA];
 #pragma unroll
-      for (int i = 0; i < KR / a_rstep; ++i) {
-        const int tok = row_tok[i0 + a_r0 + i * a_rstep];
-        const bool v = tok >= 0;
-        cp_async16(da + i * (a_rstep * 128u), a_col + static_cast<unsigned long long>(static_cast<unsigned>(v ? tok : 0)) * row_bytes_g32,
+      for (int i = 0; i < kIterA; ++i) tok[i] = row_tok[i0 + a_r0 + i * a_rstep];
+#pragma unroll
+      for (int i = 0; i < kIterA; ++i) {
+        const bool v = tok[i] >= 0;
+        cp_async16(da + i * (a_rstep * 128u), a_col + static_cast<unsigned long long>(static_cast<unsigned>(v ? tok[i] : 0)) * row_bytes_g32,
                    v ? 16u : 0u);
       }
       const uint32_t db = stage_base + b_off + b_dst0;
@@ -1350,7 +1523,7 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
       }
       b_next_kt = kt + 1;
     };
-    const bool split_batched = STRICT && KR / a_rstep <= 4 && b_fast && KR % b_rstep == 0 && KR / b_rstep <= 4;
+    const bool split_batched = STRICT && MT == 1 && KR / a_rstep <= 4 && b_fast && KR % b_rstep == 0 && KR / b_rstep <= 4;
     auto split_stage_batched = [&](int, uint32_t base) {
       uint32_t dst[8];
       bool on[8];
@@ -1405,11 +1578,12 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
         // out[e, f, g]: rows f are contiguous over g -> transpose so that 8 lanes cover 128 bytes of one row
         const uint32_t tile = pp.tiles0 + static_cast<uint32_t>(warp) * 4096u;
         const int nblk = (bn + 31) >> 5;
+        for (int mt = 0; mt < MT; ++mt)
         for (int c = half; c < nblk; c += 2) {
           const int gcol0 = g0 + c * 32;
-          warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 32), tile, lane, pp.nk > 0,
-                          [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-                            const int f = f0 + lg * 32 + row;
+          warp_block_emit(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + mt * acc_cols + static_cast<uint32_t>(c * 32), tile, lane,
+                          pp.nk > 0, [&](int row, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                            const int f = f0 + mt * kTileM + lg * 32 + row;
                             const int g = gcol0 + cj;
                             if (f < p.FG && g < p.FD) {
                               const long long off = (static_cast<long long>(e) * p.FG + f) * p.FD + g;
@@ -1420,12 +1594,13 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
         }
       } else {
         // out[e, g, f]: for a fixed g consecutive lanes (f) are already contiguous in memory
-        const int f = f0 + lg * 32 + lane;
         const int nch = bn >> 4;
+        for (int mt = 0; mt < MT; ++mt)
         for (int c = half; c < nch; c += 2) {
+          const int f = f0 + mt * kTileM + lg * 32 + lane;
           uint32_t v[16];
           if (pp.nk > 0) {
-            tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(c * 16), v);
+            tmem_ld16(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + mt * acc_cols + static_cast<uint32_t>(c * 16), v);
             tmem_ld_wait();
           } else {
 #pragma unroll
@@ -1458,6 +1633,8 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
         uint64_t bd = make_smem_desc(b_hi, seg_stride, kMnSbo, kMnLayout);
         uint64_t adl = STRICT ? make_smem_desc(a_hi + a_lo_off, seg_stride, kMnSbo, kMnLayout) : 0ull;
         uint64_t bdl = STRICT ? make_smem_desc(b_hi + b_lo_off, seg_stride, kMnSbo, kMnLayout) : 0ull;
+        // second accumulator (MT = 2): features 128..255 of the A tile, ES segments further on
+        const uint64_t a_mt_adv = (static_cast<uint32_t>(ES) * seg_stride) >> 4;
         for (int kq = 0; kq < nkq; ++kq) {
           const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
           if (STRICT) {
@@ -1466,6 +1643,7 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, 1u);
           } else {
             umma<Elem<T>::tf32>(tmem_base, ad, bd, idesc, acc);
+            if (MT == 2) umma<Elem<T>::tf32>(tmem_base + acc_cols, ad + a_mt_adv, bd, idesc, acc);
           }
           ad += k_adv; bd += k_adv; adl += k_adv; bdl += k_adv;
         }
@@ -1474,6 +1652,332 @@ __global__ void __launch_bounds__(kThreads, 2) tensor_dweight_kernel(DWeightPara
     __syncwarp();
   }
   pipe_teardown(tmem_base, tmem_cols, warp);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Fused pair  G -> S  for float32 tensors:   Mid = gather(Src) x W1[e]   (slot rows, stored),
+//                                            Dst[token rows] += Mid x W2[e]
+//   forward  : Src = X,    W1 = W_g, W2 = W_s (both EGS_W_CN)  ->  Mid = Y,  Dst = Out
+//   backward : Src = dOut, W1 = W_s, W2 = W_g (both EGS_W_NC)  ->  Mid = dY, Dst = dX
+// One CTA per (expert, 128 expert rows).  The 128 x N1 tile of Mid never leaves the SM between the two
+// contractions: the epilogue warps read it from tensor memory, store it to global memory (the backward pass
+// and the weight gradients need it) and write it into shared memory in the K-major swizzled operand format,
+// from where the second contraction consumes it.  Saves one kernel launch per pair and the re-read of Mid -
+// what the launch-latency-bound float32 configurations are made of.
+//   warps 0..7   producers: stages of (gathered Src rows, W1 tile), then stages of W2 tiles, one ring
+//   warps 8..15  epilogue : Mid tile (store + operand write), then the scatter epilogue (coalesced red.global.add)
+//   warp  16     TMEM allocation; one lane issues all tcgen05.mma
+// Conditions (checked on the host): float32, N1 a multiple of 32 and <= 256 (Mid rows are whole 128-byte
+// segments), N2 <= one tile (128 strict / 256 TF32), row pitches multiples of 16 bytes.
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t kFusedHeaderBytes = 3072;
+struct __align__(16) FusedHeader {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long acc1_done, mid_ready, acc2_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  int row_tok[kTileM];    // token row of every tile row (-1 = masked): gather source and scatter target
+  int row_slot[kTileM];   // slot row of every tile row (-1 = beyond the expert's rows)
+};
+static_assert(sizeof(FusedHeader) <= kFusedHeaderBytes, "header does not fit");
+
+template <bool STRICT>
+__global__ void __launch_bounds__(17 * 32, 1) tensor_fused_pair_kernel(FusedParams p) {
+  constexpr int ES = 4, KE = 32, UK = 8;          // float32: 32 elements per 128-byte segment, 8 per tcgen05.mma
+  constexpr int kProdWarps = 8, kEpiWarps = 8, kProdThreads = kProdWarps * 32;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  FusedHeader* hdr = reinterpret_cast<FusedHeader*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = blockIdx.y;
+  const int m0 = blockIdx.x * kTileM;
+  const bool w_nc = (p.w_layout == EGS_W_NC);
+  const int nseg_mid = p.N1 / KE;                                  // 128-byte segments per Mid row
+  const uint32_t mid_bytes = static_cast<uint32_t>(nseg_mid) * kTileM * 128u;
+  const uint32_t mid0 = smem_u32(smem_raw) + kFusedHeaderBytes;   // Mid operand tile (hi), then lo in strict mode
+  const uint32_t mid_lo_off = mid_bytes;
+  const uint32_t tiles0 = mid0 + mid_bytes * (STRICT ? 2u : 1u);  // stage ring
+  // stage layouts: phase 1 = [A hi | A lo | B hi | B lo], phase 2 = [B hi | B lo]; one stage size for both
+  const uint32_t a_bytes = kTileM * 128u;
+  const int nseg_b1 = (p.BN1 * ES + 127) / 128, nseg_b2 = (p.BN2 * ES + 127) / 128;
+  const uint32_t b1_bytes = w_nc ? static_cast<uint32_t>(p.BN1) * 128u : static_cast<uint32_t>(nseg_b1) * KE * 128u;
+  const uint32_t b2_bytes = w_nc ? static_cast<uint32_t>(p.BN2) * 128u : static_cast<uint32_t>(nseg_b2) * KE * 128u;
+  const uint32_t s1_bytes = (a_bytes + b1_bytes) * (STRICT ? 2u : 1u), s2_bytes = b2_bytes * (STRICT ? 2u : 1u);
+  const uint32_t stage_bytes = s1_bytes > s2_bytes ? s1_bytes : s2_bytes;
+  const uint32_t a_lo_off = a_bytes, b1_off = STRICT ? 2u * a_bytes : a_bytes, b1_lo_off = b1_bytes, b2_lo_off = b2_bytes;
+  const int stages = p.stages;
+  const int nk1 = (p.C1 + KE - 1) / KE, nk2 = nseg_mid;
+  const uint32_t acc1_cols = tmem_cols_for(p.BN1), acc2_cols = tmem_cols_for(p.BN2);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < acc1_cols + acc2_cols) tmem_cols <<= 1;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  // ---- set-up ----
+  if (tid < kTileM) {
+    const int m = m0 + tid;
+    int tok = -1, slot = -1;
+    if (m < p.M) {
+      const int b = m / p.K, k = m - b * p.K;
+      slot = (b * p.E + e) * p.K + k;
+      const long long t = load_index(p.Ind, p.index_dtype, slot);
+      if (t >= 0 && t < p.T) tok = b * p.T + static_cast<int>(t);
+      else if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+    }
+    hdr->row_tok[tid] = tok;
+    hdr->row_slot[tid] = slot;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), STRICT ? kProdWarps : kProdThreads);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&hdr->acc1_done), 1);
+    mbar_init(smem_u32(&hdr->mid_ready), kEpiWarps);
+    mbar_init(smem_u32(&hdr->acc2_done), 1);
+    fence_mbar_init();
+    hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
+    if (smem_misaligned(smem_raw)) {
+      hdr->abort_flag = 1u;
+      if (p.status) atomicOr(p.status, EGS_STATUS_INTERNAL);
+    }
+  }
+  const int mma_warp = kProdWarps + kEpiWarps;
+  if (warp == mma_warp) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+  const uint32_t acc1 = tmem_base, acc2 = tmem_base + acc1_cols;
+  const bool run = (hdr->abort_flag == 0u);
+  const int ntot = nk1 + nk2;
+  if (!run) {
+    // fall through to the common exit
+  } else if (warp < kProdWarps) {
+    // =========================== producers ===========================
+    const char* Src = static_cast<const char*>(p.Src);
+    const char* W1 = static_cast<const char*>(p.W1) + static_cast<long long>(e) * p.C1 * p.N1 * ES;
+    const char* W2 = static_cast<const char*>(p.W2) + static_cast<long long>(e) * p.N1 * p.N2 * ES;
+    const long long rb_src = static_cast<long long>(p.C1) * ES;    // row pitch of Src, and of W1 in NC layout
+    const long long rb_n1 = static_cast<long long>(p.N1) * ES;     // row pitch of W1 in CN layout and of W2 in NC layout
+    const long long rb_n2 = static_cast<long long>(p.N2) * ES;     // row pitch of W2 in CN layout
+    const int cc = tid & 7, r0 = tid >> 3;
+    const uint32_t rc_dst0 = static_cast<uint32_t>(r0) * 128u + (static_cast<uint32_t>(cc ^ (r0 & 7)) << 4);
+    const char* a_src[kTileM / 32];
+    uint32_t a_mask = 0;
+#pragma unroll
+    for (int i = 0; i < kTileM / 32; ++i) {
+      const int tok = hdr->row_tok[r0 + 32 * i];
+      a_src[i] = Src + (tok >= 0 ? static_cast<long long>(tok) * rb_src : 0ll) + cc * 16;
+      if (tok >= 0) a_mask |= 1u << i;
+    }
+    const int cpr1 = nseg_b1 * 8, cpr2 = nseg_b2 * 8;
+    // visits every 16-byte chunk this thread owns in stage g:  f(dst_hi_addr, src, valid, lo_offset)
+    auto for_each_chunk = [&](int g, uint32_t base, auto&& f) {
+      if (g < nk1) {
+        const long long koff = static_cast<long long>(g) * 128;
+        const bool kvalid = koff + cc * 16 < rb_src;
+#pragma unroll
+        for (int i = 0; i < kTileM / 32; ++i)
+          f(base + rc_dst0 + i * 4096u, a_src[i] + koff, kvalid && ((a_mask >> i) & 1u), a_lo_off);
+        if (w_nc) {       // W1 rows = n (N1 of them), contraction contiguous
+          for (int r = r0; r < p.BN1; r += 32)
+            f(base + b1_off + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(cc ^ (r & 7)) << 4),
+              W1 + static_cast<long long>(r) * rb_src + koff + cc * 16, kvalid && r < p.N1, b1_lo_off);
+        } else {          // W1 rows = contraction index, n contiguous
+          for (int idx = tid; idx < KE * cpr1; idx += kProdThreads) {
+            const int r = idx / cpr1, c = idx - r * cpr1;
+            f(tile_addr<true>(base + b1_off, KE * 128u, r, c), W1 + static_cast<long long>(g * KE + r) * rb_n1 + c * 16,
+              (g * KE + r) < p.C1 && c * 16 < rb_n1, b1_lo_off);
+          }
+        }
+      } else {
+        const int ks2 = g - nk1;
+        if (w_nc) {       // W2 rows = n2, contraction (N1) contiguous
+          const long long koff = static_cast<long long>(ks2) * 128;
+          for (int r = r0; r < p.BN2; r += 32)
+            f(base + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(cc ^ (r & 7)) << 4),
+              W2 + static_cast<long long>(r) * rb_n1 + koff + cc * 16, r < p.N2, b2_lo_off);
+        } else {          // W2 rows = contraction index (N1), n2 contiguous
+          for (int idx = tid; idx < KE * cpr2; idx += kProdThreads) {
+            const int r = idx / cpr2, c = idx - r * cpr2;
+            f(tile_addr<true>(base, KE * 128u, r, c), W2 + static_cast<long long>(ks2 * KE + r) * rb_n2 + c * 16, c * 16 < rb_n2,
+              b2_lo_off);
+          }
+        }
+      }
+    };
+    auto issue = [&](int g, uint32_t base) {
+      for_each_chunk(g, base, [&](uint32_t dst, const char* src, bool v, uint32_t) { cp_async16(dst, v ? src : Src, v ? 16u : 0u); });
+    };
+    bool alive = true;
+    if (!STRICT) {
+      for (int g = 0; g < ntot; ++g) {
+        const int slot = g % stages, use = g / stages;
+        if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
+        if (!alive) break;
+        issue(g, tiles0 + slot * stage_bytes);
+        cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
+      }
+    } else {
+      const int dist = stages - 1;
+      for (int g = 0; g < dist; ++g) {
+        if (g < ntot) issue(g, tiles0 + (g % stages) * stage_bytes);
+        cp_async_commit();
+      }
+      for (int gc = 0; gc < ntot; ++gc) {
+        cp_async_wait_pending(dist - 1);
+        if (alive) {
+          for_each_chunk(gc, tiles0 + (gc % stages) * stage_bytes,
+                         [&](uint32_t dst, const char*, bool, uint32_t lo_off) { split_store(dst, lo_off, lds16(dst)); });
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->full[gc % stages]));
+        }
+        const int g = gc + dist;
+        if (g < ntot && alive) {
+          const int use = g / stages;
+          if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[g % stages]), (use - 1) & 1, abort_flag, p.status, lane);
+          if (alive) issue(g, tiles0 + (g % stages) * stage_bytes);
+        }
+        cp_async_commit();
+      }
+    }
+    cp_async_wait_all();
+  } else if (warp < kProdWarps + kEpiWarps) {
+    // =========================== epilogue warps ===========================
+    const int ew = warp - kProdWarps;
+    const int lg = ew & 3, half = ew >> 2;        // TMEM lane group (= warp index modulo 4), half of the column blocks
+    const int row = lg * 32 + lane;               // tile row this thread owns in tensor memory
+    const uint32_t lane_base = static_cast<uint32_t>(lg * 32) << 16;
+    bool alive = true;
+    if (nk1 > 0) alive = mbar_wait_warp(smem_u32(&hdr->acc1_done), 0u, abort_flag, p.status, lane);
+    if (alive) {
+      tc_fence_after();
+      // (1) Mid tile: tensor memory -> shared memory in the K-major operand format (segment = 32 columns)
+      for (int c = half; c < nseg_mid; c += 2) {
+        uint32_t v[32];
+        if (nk1 > 0) {
+          tmem_ld32(acc1 + lane_base + static_cast<uint32_t>(c * 32), v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        const uint32_t seg = mid0 + static_cast<uint32_t>(c) * (kTileM * 128u) + static_cast<uint32_t>(row) * 128u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t addr = seg + (static_cast<uint32_t>(j ^ (row & 7)) << 4);
+          const uint4 x = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w) : "memory");
+          if (STRICT) split_store(addr, mid_lo_off, x);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&hdr->mid_ready));
+      // (2) the same rows go to global memory, read back from the tile so that 8 lanes cover 128 contiguous bytes
+      float* mid_out = static_cast<float*>(p.Mid);
+      const int j = lane & 7;
+      for (int c = half; c < nseg_mid; c += 2) {
+        const uint32_t seg = mid0 + static_cast<uint32_t>(c) * (kTileM * 128u);
+        uint4 x[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = lg * 32 + it * 4 + (lane >> 3);
+          x[it] = lds16(seg + static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(j ^ (r & 7)) << 4));
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = lg * 32 + it * 4 + (lane >> 3);
+          const int slot = hdr->row_slot[r];
+          if (slot >= 0) *reinterpret_cast<uint4*>(mid_out + static_cast<long long>(slot) * p.N1 + c * 32 + j * 4) = x[it];
+        }
+      }
+      // (3) scatter epilogue: the stage ring is idle once acc2_done has completed; its first 32 KB are the
+      //     warps' transpose tiles
+      alive = mbar_wait_warp(smem_u32(&hdr->acc2_done), 0u, abort_flag, p.status, lane);
+      if (alive) {
+        tc_fence_after();
+        const uint32_t tile = tiles0 + static_cast<uint32_t>(ew) * 4096u;
+        const int nblk = (p.BN2 + 31) >> 5;
+        for (int c = half; c < nblk; c += 2) {
+          warp_block_emit(acc2 + lane_base + static_cast<uint32_t>(c * 32), tile, lane, true,
+                          [&](int r, int cj, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
+                            const int tok = hdr->row_tok[lg * 32 + r];
+                            const int col = c * 32 + cj;
+                            if (tok >= 0 && col < p.N2) red4(p.Dst + static_cast<long long>(tok) * p.N2 + col, x0, x1, x2, x3);
+                          });
+        }
+      }
+    }
+  } else {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const uint32_t b_lbo = w_nc ? 16u : KE * 128u;
+      const uint32_t b_sbo = w_nc ? 1024u : 512u;
+      const uint32_t b_lay = w_nc ? kSwizzle128 : kSwizzle128Base32;
+      const uint64_t a_adv = 32u >> 4, b_adv = (w_nc ? 32u : UK * 128u) >> 4;
+      const uint32_t idesc1 = make_idesc(2u, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(p.BN1));
+      const uint32_t idesc2 = make_idesc(2u, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(p.BN2));
+      bool ok = true;
+      for (int g = 0; g < ntot && ok; ++g) {
+        const int slot = g % stages;
+        if (g == nk1) {
+          // the Mid operand tile must be complete before the second contraction starts
+          ok = mbar_wait(smem_u32(&hdr->mid_ready), 0u, abort_flag, p.status);
+          if (!ok) break;
+        }
+        ok = mbar_wait(smem_u32(&hdr->full[slot]), (g / stages) & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t base = tiles0 + slot * stage_bytes;
+        const bool ph1 = g < nk1;
+        const int ks = ph1 ? g : g - nk1;
+        const uint32_t a_hi = ph1 ? base : mid0 + static_cast<uint32_t>(ks) * (kTileM * 128u);
+        const uint32_t a_lo = ph1 ? base + a_lo_off : a_hi + mid_lo_off;
+        const uint32_t b_hi = ph1 ? base + b1_off : base;
+        const uint32_t b_lo = b_hi + (ph1 ? b1_lo_off : b2_lo_off);
+        const int krem = ph1 ? p.C1 - ks * KE : KE;
+        const int nkq = min(KE / UK, (krem + UK - 1) / UK);
+        uint64_t ad = make_smem_desc(a_hi, 16u, 1024u);
+        uint64_t adl = STRICT ? make_smem_desc(a_lo, 16u, 1024u) : 0ull;
+        uint64_t bd = make_smem_desc(b_hi, b_lbo, b_sbo, b_lay);
+        uint64_t bdl = STRICT ? make_smem_desc(b_lo, b_lbo, b_sbo, b_lay) : 0ull;
+        const uint32_t d = ph1 ? acc1 : acc2;
+        const uint32_t idesc = ph1 ? idesc1 : idesc2;
+        for (int kq = 0; kq < nkq; ++kq) {
+          const uint32_t acc = (ks > 0 || kq > 0) ? 1u : 0u;
+          if (STRICT) {
+            umma<true>(d, adl, bd, idesc, acc);
+            umma<true>(d, ad, bdl, idesc, 1u);
+            umma<true>(d, ad, bd, idesc, 1u);
+          } else {
+            umma<true>(d, ad, bd, idesc, acc);
+          }
+          ad += a_adv;
+          adl += a_adv;
+          bd += b_adv;
+          bdl += b_adv;
+        }
+        umma_commit(smem_u32(&hdr->empty[slot]));
+        if (g == nk1 - 1) umma_commit(smem_u32(&hdr->acc1_done));
+        if (g == ntot - 1) umma_commit(smem_u32(&hdr->acc2_done));
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- common exit ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == mma_warp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1545,16 +2049,24 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   static const int persist_env = getenv("EGS_B200_PERSISTENT") ? env_int("EGS_B200_PERSISTENT") : -1;
   const long long tiles1 = static_cast<long long>((p.M + kTileM - 1) / kTileM) * n_tiles * p.E;
   p.persistent = 0;
+  // direct 16-bit scatter adds go out as bulk reductions (tuning aid: EGS_B200_BULK_EPILOGUE=0 keeps the reds)
+  static const int bulk_env = getenv("EGS_B200_BULK_EPILOGUE") ? env_int("EGS_B200_BULK_EPILOGUE") : 1;
+  p.bulk_epilogue = (bulk_env && scatter && es == 2) ? 1 : 0;
   // (measured: it wins for contractions of up to four stages - the scatter of cfg4 and cfg2 - and loses for longer ones)
   if (!strict && persist_env != 0 && ((scatter && p.C * es <= 512) || persist_env == 2) && tiles1 >= 2 * kSmCount) {
     const size_t st1 = static_cast<size_t>(kTileM) * 128 + b_bytes;
-    const size_t fixed_p = kPersistHeaderBytes + kPersistMaxEpilogueWarps * 4096;
+    size_t fixed_p = kPersistHeaderBytes + kPersistMaxEpilogueWarps * 4096;
+    // 16-bit scatter: staging buffers for the bulk adds when the ring keeps three stages
+    const size_t bulk_bytes = (kPersistMaxEpilogueWarps * 2 * kBulkBufBytes + 1023) & ~static_cast<size_t>(1023);
+    const bool bulk_fits = (kSmemMaxPerCta - kPersistHeaderBytes - bulk_bytes) / st1 >= 3;
+    if (p.bulk_epilogue && bulk_fits) fixed_p = kPersistHeaderBytes + bulk_bytes;
     size_t ns = (kSmemMaxPerCta - fixed_p) / st1;
     if (ns > static_cast<size_t>(kMaxStages)) ns = kMaxStages;
     if (ns >= 3) {
       p.persistent = 1;
       p.row_tiles = 1;
       p.stages = static_cast<int>(ns);
+      if (!bulk_fits) p.bulk_epilogue = 0;
       return fixed_p + ns * st1;
     }
   }
@@ -1571,14 +2083,20 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   if (bn > cap) bn = cap;
   p.BN = bn;
   const size_t seg_stride = static_cast<size_t>(kr) * 128;
-  const size_t a_bytes = es * seg_stride;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
+  // 256-feature CTAs (two accumulators): long contractions whose grid still covers the SMs, non-strict only
+  static const int mt_env = env_int("EGS_B200_DW_ROW_TILES");
+  const long long tiles2 = static_cast<long long>((p.FG + 2 * kTileM - 1) / (2 * kTileM)) * ((p.FD + bn - 1) / bn) * p.E;
+  const bool want2 = !strict && p.FG > kTileM && tiles2 >= kSmCount && p.M >= 16 * kr && bn * 2 <= 512;
+  p.row_tiles = (mt_env == 1) ? 1 : (mt_env == 2 && !strict && p.FG > kTileM) ? 2 : (want2 ? 2 : 1);
+  const size_t a_bytes = es * seg_stride * p.row_tiles;
   const size_t stage_bytes = (a_bytes + nseg_b * seg_stride) * (strict ? 2 : 1);
   // split the contraction so that the grid fills one wave of CTAs and no CTA owns more rows than the
   // shared-memory row table holds
-  const long long tiles = static_cast<long long>((p.FG + kTileM - 1) / kTileM) * ((p.FD + bn - 1) / bn) * p.E;
-  // as many row ranges as still fit in one wave of CTAs (two CTAs per SM)
-  long long want = (static_cast<long long>(kSmCount) * 2) / tiles;
+  const int f_tile = kTileM * p.row_tiles;
+  const long long tiles = static_cast<long long>((p.FG + f_tile - 1) / f_tile) * ((p.FD + bn - 1) / bn) * p.E;
+  // as many row ranges as still fit in one wave of CTAs (two CTAs per SM with 128-feature tiles)
+  long long want = (static_cast<long long>(kSmCount) * (p.row_tiles == 2 ? 1 : 2)) / tiles;
   const long long min_splits = (p.M + kMaxRowsPerSplit - 1) / kMaxRowsPerSplit;
   if (want < min_splits) want = min_splits;
   const long long max_splits = (p.M + kr - 1) / kr;
@@ -1592,8 +2110,38 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   if (p.splits < 1) p.splits = 1;
   const size_t table_bytes = (static_cast<size_t>(rows) * 4 + 1023) & ~static_cast<size_t>(1023);
   const size_t fixed = kHeaderBytesD + table_bytes;
-  p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, true);
+  p.stages = pick_stages(fixed, stage_bytes, tiles * p.splits, p.row_tiles == 1);
   return fixed + p.stages * stage_bytes;
+}
+
+size_t configure_tensor_fused_pair(FusedParams& p, int precision) {
+  const bool strict = (precision == EGS_PREC_STRICT);
+  const size_t es = 4, ke = 32;
+  if (p.C1 < 1 || p.C1 % 4 != 0 || p.N2 < 1 || p.N2 % 4 != 0) return 0;    // 16-byte row pitches
+  if (p.N1 < 32 || p.N1 > 256 || p.N1 % 32 != 0) return 0;                 // Mid rows are whole 128-byte segments
+  const int bn2 = (p.N2 + 15) & ~15;
+  if (bn2 > (strict ? 128 : 256)) return 0;                                // one tile over N2
+  p.BN1 = p.N1;
+  p.BN2 = bn2;
+  const bool nc = (p.w_layout == EGS_W_NC);
+  const size_t a_bytes = static_cast<size_t>(kTileM) * 128;
+  const size_t nseg1 = (p.BN1 * es + 127) / 128, nseg2 = (p.BN2 * es + 127) / 128;
+  const size_t b1 = nc ? static_cast<size_t>(p.BN1) * 128 : nseg1 * ke * 128;
+  const size_t b2 = nc ? static_cast<size_t>(p.BN2) * 128 : nseg2 * ke * 128;
+  const size_t s1 = (a_bytes + b1) * (strict ? 2 : 1), s2 = b2 * (strict ? 2 : 1);
+  const size_t stage_bytes = s1 > s2 ? s1 : s2;
+  const size_t mid = static_cast<size_t>(p.N1 / 32) * kTileM * 128 * (strict ? 2 : 1);
+  const size_t fixed = kFusedHeaderBytes + mid;
+  if (fixed + 2 * stage_bytes > kSmemMaxPerCta) return 0;
+  size_t ns = (kSmemMaxPerCta - fixed) / stage_bytes;
+  const size_t ntot = static_cast<size_t>((p.C1 + 31) / 32 + p.N1 / 32);
+  if (ns > ntot) ns = ntot;
+  if (ns > static_cast<size_t>(kMaxStages)) ns = kMaxStages;
+  static const int env = env_int("EGS_B200_STAGES");
+  if (env >= 2 && static_cast<size_t>(env) < ns) ns = env;
+  if (ns < 2 || ns * stage_bytes < 8u * 4096u) return 0;                   // the ring doubles as the transpose tiles
+  p.stages = static_cast<int>(ns);
+  return fixed + ns * stage_bytes;
 }
 
 // The opt-in to large dynamic shared memory is per kernel function: done once, for the maximum.
@@ -1670,13 +2218,19 @@ cudaError_t launch_tensor_rowgemm(const RowGemmParams& p, bool scatter, int dtyp
 }
 
 cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precision, size_t smem_bytes, cudaStream_t st) {
-  dim3 grid((p.FG + kTileM - 1) / kTileM, (p.FD + p.BN - 1) / p.BN, p.E * p.splits);
+  const int f_tile = kTileM * p.row_tiles;
+  dim3 grid((p.FG + f_tile - 1) / f_tile, (p.FD + p.BN - 1) / p.BN, p.E * p.splits);
   dim3 block(kThreads);
   cudaError_t err = cudaSuccess;
-#define EGS_LAUNCH(TY, STRICT)                                                          \
-  do {                                                                                  \
-    err = (ensure_smem_optin<tensor_dweight_kernel<TY, STRICT>>());                        \
-    if (err == cudaSuccess) tensor_dweight_kernel<TY, STRICT><<<grid, block, smem_bytes, st>>>(p); \
+#define EGS_LAUNCH_D(TY, STRICT, MTV)                                                           \
+  do {                                                                                          \
+    err = (ensure_smem_optin<tensor_dweight_kernel<TY, STRICT, MTV>>());                        \
+    if (err == cudaSuccess) tensor_dweight_kernel<TY, STRICT, MTV><<<grid, block, smem_bytes, st>>>(p); \
+  } while (0)
+#define EGS_LAUNCH(TY, STRICT)                                   \
+  do {                                                           \
+    if (p.row_tiles == 2 && !STRICT) EGS_LAUNCH_D(TY, false, 2); \
+    else EGS_LAUNCH_D(TY, STRICT, 1);                            \
   } while (0)
   if (dtype == EGS_F32) {
     if (precision == EGS_PREC_STRICT) EGS_LAUNCH(float, true);
@@ -1687,6 +2241,23 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
     EGS_LAUNCH(__nv_bfloat16, false);
   }
 #undef EGS_LAUNCH
+#undef EGS_LAUNCH_D
+  if (err != cudaSuccess) return err;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t smem_bytes, cudaStream_t st) {
+  dim3 grid((p.M + kTileM - 1) / kTileM, p.E);
+  dim3 block(17 * 32);
+  cudaError_t err;
+  if (precision == EGS_PREC_STRICT) {
+    err = ensure_smem_optin<tensor_fused_pair_kernel<true>>();
+    if (err == cudaSuccess) tensor_fused_pair_kernel<true><<<grid, block, smem_bytes, st>>>(p);
+  } else {
+    err = ensure_smem_optin<tensor_fused_pair_kernel<false>>();
+    if (err == cudaSuccess) tensor_fused_pair_kernel<false><<<grid, block, smem_bytes, st>>>(p);
+  }
   if (err != cudaSuccess) return err;
   count_launch();
   return cudaGetLastError();

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gather_gemm", "gemm_scatter", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
+__all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
            "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
@@ -230,6 +230,59 @@ def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=
     if _state["debug"]:
         check_status(dev)
     return out
+
+
+def fused_pair_eligible(C1: int, N1: int, N2: int, dtype: torch.dtype, *, w_layout="cn", precision=None) -> bool:
+    """True when :func:`gather_scatter_pair` has a kernel for this shape on the current device (float32, the
+    middle width a multiple of 32 and at most 256, the output width within one tile, tiles fitting in shared memory)."""
+    if dtype != torch.float32 or _state["path"] == "generic":
+        return False
+    lib = _lib.load()
+    prec, _ = _enums(precision, None)
+    wl = _lib.W_CN if w_layout == "cn" else _lib.W_NC
+    return bool(lib.egs_fused_pair_eligible(int(C1), int(N1), int(N2), wl, dtype_to_type_id(dtype), prec))
+
+
+def gather_scatter_pair(Src, W1, W2, Ind, *, w_layout="cn", out=None, precision=None):
+    """Operators G and S back to back in one kernel: ``Mid = gather(Src) @ W1v[e]`` (returned, [B,E,K,N1]) and
+    ``Dst[b, Ind[b,e,k], :] += Mid[b,e,k,:] @ W2v[e]`` ([B,T,N2]); both weights in the same layout.
+
+    Forward: ``gather_scatter_pair(X, W_g, W_s, Ind)`` -> (Y, Out).  Backward: ``gather_scatter_pair(dOut, W_s, W_g,
+    Ind, w_layout="nc")`` -> (dY, dX).  ``out=None`` allocates and zero-fills Dst; a given ``out`` is added to.
+    Raises when the shape is not eligible (see :func:`fused_pair_eligible`): callers then use the two operators."""
+    lib = _lib.load()
+    if Src.dim() != 3 or W1.dim() != 3 or W2.dim() != 3 or Ind.dim() != 3:
+        raise ValueError("expected Src[B,T,C1], W1[E,.,.], W2[E,.,.], Ind[B,E,K]")
+    dev = _require_cuda(Src, W1, W2, Ind)
+    if W1.dtype != Src.dtype or W2.dtype != Src.dtype:
+        raise ValueError("Src, W1 and W2 must have the same dtype")
+    dt = dtype_to_type_id(Src.dtype)
+    E, C1, N1, wl = _w_dims(W1, w_layout)
+    E2, N1b, N2, _ = _w_dims(W2, w_layout)
+    B, T, Cx = Src.shape
+    Bi, Ei, K = Ind.shape
+    if Cx != C1 or E2 != E or N1b != N1 or Ei != E or Bi != B:
+        raise ValueError(f"shape mismatch: Src{tuple(Src.shape)} W1{tuple(W1.shape)} W2{tuple(W2.shape)} "
+                         f"Ind{tuple(Ind.shape)} ({w_layout})")
+    Sc, W1c, W2c = Src.contiguous(), W1.contiguous(), W2.contiguous()
+    Ic, it = _index_tensor(Ind)
+    prec, _ = _enums(precision, None)
+    with torch.cuda.device(dev):
+        Mid = torch.empty((B, E, K, N1), device=dev, dtype=Src.dtype)
+        zero = 1
+        if out is None:
+            out = torch.empty((B, T, N2), device=dev, dtype=Src.dtype)
+        else:
+            if tuple(out.shape) != (B, T, N2) or out.dtype != Src.dtype or not out.is_contiguous():
+                raise ValueError("out must be a contiguous [B,T,N2] tensor of Src's dtype")
+            zero = 0
+        rc = lib.egs_gather_scatter_pair(Sc.data_ptr(), W1c.data_ptr(), W2c.data_ptr(), Ic.data_ptr(), Mid.data_ptr(),
+                                         out.data_ptr(), B, T, E, K, C1, N1, N2, wl, zero, dt, it, prec,
+                                         _status_word(dev).data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "egs_gather_scatter_pair")
+    if _state["debug"]:
+        check_status(dev)
+    return Mid, out
 
 
 def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path=None):

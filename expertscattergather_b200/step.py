@@ -15,9 +15,12 @@ from . import ops
 
 __all__ = ["train_step"]
 
+_SM_COUNT = 148
+
 
 def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.Tensor, G: torch.Tensor,
-               on_weight_grad: Optional[Callable[[str, torch.Tensor], None]] = None, overlap: bool = True) -> dict:
+               on_weight_grad: Optional[Callable[[str, torch.Tensor], None]] = None, overlap: bool = True,
+               fused_pairs: bool = True) -> dict:
     """X [B,T,I], Wg [E,I,J], Ws [E,J,I], Ind [B,E,K], G [B,T,I] (the gradient of the loss w.r.t. Out).
 
     Returns Y, Out, dY, dX, dWg, dWs.  Equivalent to
@@ -27,7 +30,8 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     fills of Out and dX (float32 tensors; 16-bit outputs are initialised by the scatter's own planning step) and
     the two weight-gradient kernels, each started as soon as its inputs exist.  With ``on_weight_grad`` (the
     data-parallel case) everything stays on one stream in an order that puts both weight gradients, and with them
-    the start of their reductions, before the last scatter.
+    the start of their reductions, before the last scatter.  With ``fused_pairs`` float32 shapes that the fused
+    pair kernel takes run G -> S and dY -> dX as one kernel each.
     """
     T = X.shape[1]
     if on_weight_grad is not None:
@@ -55,6 +59,12 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     main = torch.cuda.current_stream(dev)
     side = ops.side_stream(dev)
     prefill = X.dtype == torch.float32
+    I, J = X.shape[2], Wg.shape[2]
+    # one CTA per (expert, 128 expert rows) and one CTA per SM: the fused kernel pays while its grid is a single wave
+    pair_ctas = Wg.shape[0] * ((X.shape[0] * Ind.shape[2] + 127) // 128)
+    fused = (fused_pairs and prefill and pair_ctas <= _SM_COUNT
+             and ops.fused_pair_eligible(I, J, I, X.dtype, w_layout="cn")
+             and ops.fused_pair_eligible(I, J, I, X.dtype, w_layout="nc"))
     Out = dX = None
     side.wait_stream(main)                                             # fork
     if prefill:
@@ -62,8 +72,27 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         dX = torch.empty_like(X, memory_format=torch.contiguous_format)
         with torch.cuda.stream(side):
             ops.fill_zero(Out)
+            out_filled = side.record_event()
             ops.fill_zero(dX)
         fills_done = side.record_event()
+    if prefill and fused:
+        # float32 shapes the fused pair kernel takes: two kernels on the critical chain instead of four
+        main.wait_event(out_filled)
+        Y, Out = ops.gather_scatter_pair(X, Wg, Ws, Ind, w_layout="cn", out=Out)      # gather + scatter forward
+        fwd_done = main.record_event()
+        with torch.cuda.stream(side):
+            side.wait_event(fwd_done)
+            dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")                  # scatter backward: dW_s
+            dWs.record_stream(main)
+        main.wait_event(fills_done)
+        dY, dX = ops.gather_scatter_pair(G, Ws, Wg, Ind, w_layout="nc", out=dX)       # dY and dX
+        dy_ready = main.record_event()
+        with torch.cuda.stream(side):
+            side.wait_event(dy_ready)
+            dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")               # gather backward: dW_g
+            dWg.record_stream(main)
+        main.wait_stream(side)
+        return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
     Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                     # gather forward
     if prefill:
         main.wait_event(fills_done)

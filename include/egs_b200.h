@@ -144,6 +144,26 @@ int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* I
 /* Capacity of the built-in scratch in float32 elements.  No counterpart in the reference. */
 size_t egs_static_scratch_max_elements(void);
 
+/* Fused pair G -> S in ONE kernel (float32 tensors, tensor-core path only):
+ *     Mid[slot rows, N1]  = gather(Src)[slot rows, C1] x W1[e]          (overwritten; what egs_gather_gemm computes)
+ *     Dst[token rows, N2] += Mid x W2[e]                                 (what egs_gemm_scatter computes)
+ * The 128 x N1 tile of Mid stays on the SM between the two contractions; it is also stored, because the backward
+ * pass and the weight gradients read it.  Both weights are given in the same layout:
+ *   forward  (egs/triton_kernels.py:382-390 followed by :464-472): Src = X, W1 = W_g [E,I,J], W2 = W_s [E,J,I],
+ *            w_layout = EGS_W_CN, C1 = I, N1 = J, N2 = I  ->  Mid = Y, Dst = Out
+ *   backward (egs/triton_kernels.py:500-508 followed by :416-424): Src = dOut, W1 = W_s [E,J,I], W2 = W_g [E,I,J],
+ *            w_layout = EGS_W_NC, C1 = I, N1 = J, N2 = I  ->  Mid = dY, Dst = dX
+ * The reference launches the two kernels of each pair separately; results equal those of the two separate calls
+ * up to the order of the float32 additions into Dst.  zero_output as in egs_gemm_scatter.
+ * Returns EGS_ERR_UNSUPPORTED when egs_fused_pair_eligible says 0: the caller then makes the two separate calls. */
+int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, const void* Ind, void* Mid, void* Dst,
+                            int64_t B, int64_t T, int64_t E, int64_t K, int64_t C1, int64_t N1, int64_t N2,
+                            int w_layout, int zero_output, int dtype, int index_dtype, int precision,
+                            int32_t* status_word, void* cuda_stream);
+/* 1 if egs_gather_scatter_pair takes this shape on the current device: float32, sm_100, N1 a multiple of 32 and
+ * <= 256, N2 within one tile (128 strict / 256 TF32), 16-byte row pitches, and the tiles fit in shared memory. */
+int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision);
+
 /* 1 if EGS_PATH_AUTO would take the tcgen05 tensor-core kernels for this operator and shape, else 0.
  * op: 0 = G, 1 = S, 2 = D (for D pass C=FG, N=FD).  No reference counterpart (diagnostic). */
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers,

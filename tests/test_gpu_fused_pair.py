@@ -1,0 +1,119 @@
+"""The fused pair kernel (gather-GEMM whose output tile feeds the GEMM-scatter without leaving the SM) against the
+CPU oracle and against the two separate operators.  Called through the C ABI (egs_gather_scatter_pair)."""
+import numpy as np
+import pytest
+import torch
+
+from expertscattergather_b200 import ops, workloads
+from expertscattergather_b200.workloads import Workload
+from gpu_util import compare_step, gpu_step, to_dev, tol_for
+from oracle import egs_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair_both_ways(d, precision):
+    """Forward pair (X -> Y -> Out) and backward pair (G -> dY -> dX) through the fused kernel."""
+    Y, Out = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"], w_layout="cn", precision=precision)
+    dY, dX = ops.gather_scatter_pair(d["G"], d["Ws"], d["Wg"], d["Ind"], w_layout="nc", precision=precision)
+    return Y, Out, dY, dX
+
+
+# (B, T, E, K, I, J): I = outer width (C1 and N2), J = middle width (N1, a multiple of 32)
+SHAPES = [
+    (16, 256, 32, 32, 128, 64),      # the default float32 configuration's operator shape
+    (3, 50, 5, 7, 128, 64),          # ragged rows: B*K = 21 of 128 tile rows
+    (5, 300, 3, 60, 100, 32),        # contraction not a multiple of 32, N2 = 100 (not a multiple of 16)
+    (2, 64, 2, 40, 36, 64),          # two stages of contraction, one of them partial
+    (9, 40, 4, 33, 64, 32),          # B*K = 297: three row tiles, the last one partial
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("precision", ["strict", "tf32"])
+def test_pair_matches_oracle(cuda_device, shape, precision):
+    B, T, E, K, I, J = shape
+    if not ops.fused_pair_eligible(I, J, I, torch.float32, precision=precision):
+        pytest.skip("shape not taken by the fused kernel at this precision")
+    w = Workload("pair", B, T, E, K, I, J, torch.float32, "distinct" if K <= T else "replace", 77 + B)
+    ins = workloads.make_inputs(w)
+    ref = orc.torch_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    ops.reset_status()
+    Y, Out, dY, dX = _pair_both_ways(to_dev(ins, cuda_device), precision)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = {"Y": Y.cpu(), "Out": Out.cpu(), "dY": dY.cpu(), "dX": dX.cpu()}
+    compare_step(got, ref, tol_for(torch.float32, precision), keys=("Y", "Out", "dY", "dX"), what=f"pair {shape} {precision}")
+
+
+@pytest.mark.parametrize("index", ["distinct", "replace", "zipf"])
+def test_pair_is_bit_exact_on_integer_valued_inputs(cuda_device, index):
+    """Small-integer inputs make every product and sum exact: the fused kernel, the separate operators and the
+    numpy oracle must agree bit for bit, collisions included."""
+    w = Workload("pair-int", 4, 48, 6, 24, 64, 32, torch.float32, index, 5)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    d = to_dev(ins, cuda_device)
+    for precision in ("strict", "tf32"):
+        Y, Out, dY, dX = _pair_both_ways(d, precision)
+        Yr = orc.np_gather(ins["X"], ins["Wg"], ins["Ind"])
+        assert np.array_equal(Y.cpu().double().numpy(), Yr)
+        assert np.array_equal(Out.cpu().double().numpy(), orc.np_scatter(Yr, ins["Ws"], ins["Ind"], 48))
+        assert torch.equal(Y, ops.gather_gemm(d["X"], d["Wg"], d["Ind"], precision=precision))
+        assert torch.equal(Out, ops.gemm_scatter(Y, d["Ws"], d["Ind"], 48, precision=precision))
+        assert torch.equal(dY, ops.gather_gemm(d["G"], d["Ws"], d["Ind"], w_layout="nc", precision=precision))
+        assert torch.equal(dX, ops.gemm_scatter(dY, d["Wg"], d["Ind"], 48, w_layout="nc", precision=precision))
+
+
+def test_pair_adds_into_a_given_output_and_zero_fills_otherwise(cuda_device):
+    w = Workload("pair-acc", 2, 32, 3, 8, 32, 32, torch.float32, "distinct", 9)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    d = to_dev(ins, cuda_device)
+    _, Out = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"])
+    base = torch.full_like(Out, 3.0)
+    _, Out2 = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"], out=base)
+    assert Out2 is base
+    assert torch.equal(Out2, Out + 3.0)
+    _, Out3 = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"])      # fresh output: zero-filled again
+    assert torch.equal(Out3, Out)
+
+
+def test_pair_skips_and_reports_out_of_range_indices(cuda_device):
+    w = Workload("pair-oob", 2, 40, 3, 6, 32, 32, torch.float32, "distinct", 11)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    bad = ins["Ind"].clone()
+    bad[1, 2, 3] = 40
+    bad[0, 0, 0] = -1
+    d = to_dev(ins, cuda_device)
+    ops.reset_status()
+    Y, Out = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], bad.to(cuda_device))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="outside"):
+        ops.check_status()
+    Yref = torch.from_numpy(orc.np_gather(ins["X"], ins["Wg"], ins["Ind"])).float()
+    Yref[1, 2, 3] = 0
+    Yref[0, 0, 0] = 0
+    assert torch.equal(Y.cpu(), Yref)
+    assert np.array_equal(Out.cpu().double().numpy(), orc.np_scatter(Yref, ins["Ws"], bad.clamp(0, 39), 40))
+
+
+def test_ineligible_shapes_are_refused_not_miscomputed(cuda_device):
+    assert not ops.fused_pair_eligible(128, 48, 128, torch.float32)            # middle width not a multiple of 32
+    assert not ops.fused_pair_eligible(128, 64, 128, torch.bfloat16)           # 16-bit tensors
+    assert not ops.fused_pair_eligible(128, 64, 512, torch.float32)            # output wider than one tile
+    X = torch.zeros(1, 8, 128, device=cuda_device)
+    W1 = torch.zeros(2, 128, 48, device=cuda_device)
+    W2 = torch.zeros(2, 48, 128, device=cuda_device)
+    Ind = torch.zeros(1, 2, 4, dtype=torch.int64, device=cuda_device)
+    with pytest.raises(ValueError, match="not eligible"):
+        ops.gather_scatter_pair(X, W1, W2, Ind)
+
+
+def test_train_step_uses_the_pair_on_the_float32_configurations(cuda_device):
+    """The explicit step takes the fused kernel where it is eligible: fewer launches, same results."""
+    ins = workloads.make_inputs(workloads.WORKLOADS["cfg1-T256"])
+    ref = orc.torch_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    n0 = ops.launch_count()
+    got = gpu_step(ins, cuda_device, "auto", "strict")
+    launches = ops.launch_count() - n0
+    compare_step(got, ref, 1e-5, what="cfg1-T256 fused step")
+    assert launches <= 8, launches      # 2 fills + 2 pair kernels + 2 weight gradients (+ their fills)
