@@ -28,14 +28,14 @@ from expertscattergather_b200 import workloads as wl  # noqa: E402
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels of one operator call, from the ncu
 # captures summarised under profiles/ (bytes per routed slot of the captured case; scaled by the slots of the run).
 NCU_TRAFFIC_PER_SLOT = {
-    ("scatter_fwd", "cfg1-T16384"): (75.4e6 + 13.6e6) / 16384,      # fill_zero + scatter kernel
-    ("gather_bwd_dX", "cfg1-T16384"): (75.1e6 + 13.6e6) / 16384,
-    ("scatter_fwd", "cfg4"): (331.5e6 + 113.5e6) / 262144,          # captured at B=64
-    ("gather_bwd_dX", "cfg4"): (327.9e6 + 114.4e6) / 262144,
-    ("scatter_bwd_dW", "cfg4"): (370.4e6 + 23.7e6) / 262144,
-    ("gather_bwd_dW", "cfg4"): (368.6e6 + 23.3e6) / 262144,
-    ("gather_fwd", "cfg4"): (265.5e6 + 113.7e6) / 262144,
-    ("scatter_bwd_dY", "cfg4"): (272.8e6 + 110.5e6) / 262144,
+    ("pair_fwd", "cfg1-T16384"): (75.96e6 + 18.61e6) / 16384,       # fill_zero + fused pair kernel
+    ("pair_bwd", "cfg1-T16384"): (75.08e6 + 18.61e6) / 16384,
+    ("scatter_fwd", "cfg4"): (326.6e6 + 110.4e6) / 262144,          # captured at B=64
+    ("gather_bwd_dX", "cfg4"): (326.8e6 + 111.0e6) / 262144,
+    ("scatter_bwd_dW", "cfg4"): (368.4e6 + 23.1e6) / 262144,
+    ("gather_bwd_dW", "cfg4"): (368.5e6 + 23.0e6) / 262144,
+    ("gather_fwd", "cfg4"): (265.6e6 + 114.5e6) / 262144,
+    ("scatter_bwd_dY", "cfg4"): (260.5e6 + 113.1e6) / 262144,
 }
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "gather+scatter fwd+bwd routed tokens/s"
@@ -180,6 +180,9 @@ def op_work(w, B, U, op):
         return fl, U * w.I * s + WB + 8 * N + N * w.J * s
     if op in ("scatter_fwd", "gather_bwd_dX"):
         return fl, N * w.J * s + WB + 8 * N + B * w.T * w.I * s
+    if op in ("pair_fwd", "pair_bwd"):
+        # fused G -> S: token rows read once, both weights, the middle tensor written once, the output written once
+        return 2 * fl, U * w.I * s + 2 * WB + 8 * N + N * w.J * s + B * w.T * w.I * s
     return fl, U * w.I * s + N * w.J * s + 8 * N + WB      # dW_g, dW_s
 
 
@@ -209,7 +212,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
     from expertscattergather_b200 import distributed as egd, ops
-    from expertscattergather_b200.step import train_step
+    from expertscattergather_b200.step import takes_fused_pairs, train_step
     import expertscattergather_b200 as egs
 
     rank, world, local = egd.init_from_env()
@@ -341,14 +344,23 @@ def main():
         U = wl.algorithmic_work(w, Ind=host[passes.index(w)]["Ind"], B=b)["U"]
         Y = ops.gather_gemm(d["X"], d["Wg"], d["Ind"])
         dY = ops.gather_gemm(d["G"], d["Ws"], d["Ind"], w_layout="nc")
-        calls = {
-            "gather_fwd": lambda: ops.gather_gemm(d["X"], d["Wg"], d["Ind"]),
-            "scatter_fwd": lambda: ops.gemm_scatter(Y, d["Ws"], d["Ind"], w.T),
-            "scatter_bwd_dY": lambda: ops.gather_gemm(d["G"], d["Ws"], d["Ind"], w_layout="nc"),
-            "scatter_bwd_dW": lambda: ops.dweight(d["G"], Y, d["Ind"], out_layout="direct_rows"),
-            "gather_bwd_dX": lambda: ops.gemm_scatter(dY, d["Wg"], d["Ind"], w.T, w_layout="nc"),
-            "gather_bwd_dW": lambda: ops.dweight(d["X"], dY, d["Ind"]),
-        }
+        if takes_fused_pairs(d["X"], d["Wg"], d["Ind"]):
+            # the step runs each pair as one fused kernel: time what it runs
+            calls = {
+                "pair_fwd": lambda: ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"]),
+                "scatter_bwd_dW": lambda: ops.dweight(d["G"], Y, d["Ind"], out_layout="direct_rows"),
+                "pair_bwd": lambda: ops.gather_scatter_pair(d["G"], d["Ws"], d["Wg"], d["Ind"], w_layout="nc"),
+                "gather_bwd_dW": lambda: ops.dweight(d["X"], dY, d["Ind"]),
+            }
+        else:
+            calls = {
+                "gather_fwd": lambda: ops.gather_gemm(d["X"], d["Wg"], d["Ind"]),
+                "scatter_fwd": lambda: ops.gemm_scatter(Y, d["Ws"], d["Ind"], w.T),
+                "scatter_bwd_dY": lambda: ops.gather_gemm(d["G"], d["Ws"], d["Ind"], w_layout="nc"),
+                "scatter_bwd_dW": lambda: ops.dweight(d["G"], Y, d["Ind"], out_layout="direct_rows"),
+                "gather_bwd_dX": lambda: ops.gemm_scatter(dY, d["Wg"], d["Ind"], w.T, w_layout="nc"),
+                "gather_bwd_dW": lambda: ops.dweight(d["X"], dY, d["Ind"]),
+            }
         for op, fn in calls.items():
             ms = time_op(fn, reps)
             fl, by = op_work(w, b, U, op)

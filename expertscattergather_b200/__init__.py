@@ -11,11 +11,11 @@ from __future__ import annotations
 
 import sys
 
-from .torch_interface import ExpertGather, ExpertScatter
+from .torch_interface import ExpertGather, ExpertGatherScatter, ExpertScatter
 from .kernels import ExpertGatherFunction, ExpertScatterFunction, create_kernels
 from . import ops
 
-__all__ = ["ExpertGather", "ExpertScatter", "ExpertGatherFunction", "ExpertScatterFunction", "create_kernels",
+__all__ = ["ExpertGather", "ExpertScatter", "ExpertGatherScatter", "ExpertGatherFunction", "ExpertScatterFunction", "create_kernels",
            "ops", "install_as_egs"]
 __version__ = "0.1.0"
 

@@ -20,7 +20,7 @@ import torch
 
 from . import ops
 
-__all__ = ["create_kernels", "ExpertGatherFunction", "ExpertScatterFunction", "dtype_to_type_id",
+__all__ = ["create_kernels", "ExpertGatherFunction", "ExpertScatterFunction", "ExpertGatherScatterFunction", "dtype_to_type_id",
            "expert_gather_forward_call", "expert_gather_backward_call", "expert_scatter_forward_call",
            "expert_scatter_backward_call", "OP_NAMESPACE"]
 
@@ -185,3 +185,44 @@ class ExpertScatterFunction(torch.autograd.Function):
         Y, W, Ind = ctx.saved_tensors
         grad_Y, grad_W = expert_scatter_backward_call(Y, W, Ind, grad_X, ctx.dtype)
         return grad_Y, grad_W, None, None, None
+
+
+class ExpertGatherScatterFunction(torch.autograd.Function):
+    """Gather followed by scatter with the same ``Ind`` - the way the two operators are used in a model
+    (reference: ``README.md:23-32``) - as one autograd node: ``Out = scatter(gather(X, W_g), W_s)``.
+
+    ``apply(X, W_g, W_s, Ind)`` with X [B,T,I], W_g [E,I,J], W_s [E,J,I], Ind [B,E,K] -> Out [B,T,I].
+    Where the fused kernel pays (float32, single-wave grids: ``ops.fused_pair_preferred``) the forward pass is one
+    kernel (Y is written once, for the backward pass, and consumed from shared memory) and so is dY -> dX of the
+    backward pass; otherwise each pass runs the two separate operators.  The weight gradients are the same two
+    contractions as in ``ExpertGatherFunction`` / ``ExpertScatterFunction`` and run next to dY -> dX on the helper
+    stream.  backward returns ``(grad_X, grad_W_g, grad_W_s, None)`` and always computes all three.
+    """
+
+    @staticmethod
+    def forward(ctx, X, Wg, Ws, Ind):
+        X, Wg, Ws = X.contiguous(), Wg.contiguous(), Ws.contiguous()
+        ctx.fused = ops.fused_pair_preferred(X, Wg, Ind)
+        if ctx.fused:
+            Y, Out = ops.gather_scatter_pair(X, Wg, Ws, Ind, w_layout="cn")
+        else:
+            Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")
+            Out = ops.gemm_scatter(Y, Ws, Ind, X.shape[1], w_layout="cn")
+        ctx.save_for_backward(X, Wg, Ws, Ind, Y)
+        return Out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        X, Wg, Ws, Ind, Y = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        grad_Ws = _weight_grad_on_side_stream(grad_out, Y, Ind, "direct_rows")       # needs only dOut and Y
+        if ctx.fused:
+            dY, grad_X = ops.gather_scatter_pair(grad_out, Ws, Wg, Ind, w_layout="nc")
+        else:
+            dY = ops.gather_gemm(grad_out, Ws, Ind, w_layout="nc")
+            grad_X = None
+        grad_Wg = _weight_grad_on_side_stream(X, dY, Ind, "gathered_rows")
+        if grad_X is None:
+            grad_X = ops.gemm_scatter(dY, Wg, Ind, X.shape[1], w_layout="nc")
+        _join_side(grad_X)
+        return grad_X, grad_Wg, grad_Ws, None

@@ -13,11 +13,13 @@ import torch
 
 from . import _lib
 
-__all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
+__all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "fused_pair_preferred", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
            "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
 _PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR}
+_SM_COUNT = 148     # B200
+
 _state = {
     "precision": os.environ.get("EGS_B200_PRECISION", "strict").lower(),
     "path": os.environ.get("EGS_B200_PATH", "auto").lower(),
@@ -241,6 +243,18 @@ def fused_pair_eligible(C1: int, N1: int, N2: int, dtype: torch.dtype, *, w_layo
     prec, _ = _enums(precision, None)
     wl = _lib.W_CN if w_layout == "cn" else _lib.W_NC
     return bool(lib.egs_fused_pair_eligible(int(C1), int(N1), int(N2), wl, dtype_to_type_id(dtype), prec))
+
+
+def fused_pair_preferred(X: torch.Tensor, Wg: torch.Tensor, Ind: torch.Tensor) -> bool:
+    """Whether gather -> scatter over these tensors should run as the fused kernel: float32, a shape the kernel
+    takes in both weight layouts, and a grid of at most one wave (one CTA per (expert, 128 expert rows) and per SM;
+    beyond that the two separate kernels, which fit two CTAs per SM, measured faster)."""
+    if X.dtype != torch.float32 or not X.is_cuda:
+        return False
+    I, J = X.shape[2], Wg.shape[2]
+    pair_ctas = Wg.shape[0] * ((X.shape[0] * Ind.shape[2] + 127) // 128)
+    return (pair_ctas <= _SM_COUNT and fused_pair_eligible(I, J, I, X.dtype, w_layout="cn")
+            and fused_pair_eligible(I, J, I, X.dtype, w_layout="nc"))
 
 
 def gather_scatter_pair(Src, W1, W2, Ind, *, w_layout="cn", out=None, precision=None):

@@ -13,9 +13,18 @@ import torch
 
 from . import ops
 
-__all__ = ["train_step"]
+__all__ = ["train_step", "takes_fused_pairs"]
 
-_SM_COUNT = 148
+
+
+def _is_capturing(stream: "torch.cuda.Stream") -> bool:
+    with torch.cuda.stream(stream):
+        return bool(torch.cuda.is_current_stream_capturing())
+
+
+def takes_fused_pairs(X: torch.Tensor, Wg: torch.Tensor, Ind: torch.Tensor) -> bool:
+    """Whether :func:`train_step` runs G -> S and dY -> dX as one fused kernel each for these tensors."""
+    return ops.fused_pair_preferred(X, Wg, Ind)
 
 
 def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.Tensor, G: torch.Tensor,
@@ -59,18 +68,19 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     main = torch.cuda.current_stream(dev)
     side = ops.side_stream(dev)
     prefill = X.dtype == torch.float32
-    I, J = X.shape[2], Wg.shape[2]
-    # one CTA per (expert, 128 expert rows) and one CTA per SM: the fused kernel pays while its grid is a single wave
-    pair_ctas = Wg.shape[0] * ((X.shape[0] * Ind.shape[2] + 127) // 128)
-    fused = (fused_pairs and prefill and pair_ctas <= _SM_COUNT
-             and ops.fused_pair_eligible(I, J, I, X.dtype, w_layout="cn")
-             and ops.fused_pair_eligible(I, J, I, X.dtype, w_layout="nc"))
+    fused = fused_pairs and prefill and takes_fused_pairs(X, Wg, Ind)
     Out = dX = None
-    side.wait_stream(main)                                             # fork
     if prefill:
-        Out = torch.empty((X.shape[0], T, Ws.shape[2]), device=dev, dtype=X.dtype)
-        dX = torch.empty_like(X, memory_format=torch.contiguous_format)
+        # The two outputs are allocated and zero-filled on the side stream, from its own memory pool: nothing ties
+        # the fills to work already queued on the main stream (the tail of the previous step), so they run under
+        # it.  Inside a stream capture the side stream first has to join the capture through the main stream.
+        if _is_capturing(main) and not _is_capturing(side):
+            side.wait_stream(main)
         with torch.cuda.stream(side):
+            Out = torch.empty((X.shape[0], T, Ws.shape[2]), device=dev, dtype=X.dtype)
+            dX = torch.empty_like(X, memory_format=torch.contiguous_format)
+            Out.record_stream(main)
+            dX.record_stream(main)
             ops.fill_zero(Out)
             out_filled = side.record_event()
             ops.fill_zero(dX)

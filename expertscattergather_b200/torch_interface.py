@@ -14,9 +14,9 @@ import math
 import torch
 from torch import nn
 
-from .kernels import ExpertGatherFunction, ExpertScatterFunction, create_kernels
+from .kernels import ExpertGatherFunction, ExpertGatherScatterFunction, ExpertScatterFunction, create_kernels
 
-__all__ = ["ExpertGather", "ExpertScatter"]
+__all__ = ["ExpertGather", "ExpertScatter", "ExpertGatherScatter"]
 
 
 class ExpertGather(nn.Module):
@@ -78,3 +78,25 @@ class ExpertScatter(nn.Module):
         if self.bias is not None:
             out = out + self.bias   # broadcasts like the reference's expression: needs E == B or E == 1
         return out
+
+
+class ExpertGatherScatter(nn.Module):
+    """The gather -> scatter block of a model as one module: ``forward(x [B,T,I], Ind [B,E,K]) -> [B,T,I]``, equal to
+    ``scatter(gather(x, Ind), Ind, T)`` of an ``ExpertGather(E, I, J)`` and an ``ExpertScatter(E, J, I)`` (the usage
+    the reference's ``README.md:23-32`` shows).  The two sub-modules are ordinary ``ExpertGather`` / ``ExpertScatter``
+    instances (``.gather``, ``.scatter``), so their state dicts interchange with separately built ones.
+
+    Without biases the block runs as one autograd node (``ExpertGatherScatterFunction``), which uses the fused
+    kernel where it applies; with a bias on either side it falls back to calling the two sub-modules.
+    No counterpart class in the reference.
+    """
+
+    def __init__(self, E: int, I: int, J: int, bias: bool = False):
+        super().__init__()
+        self.gather = ExpertGather(E, I, J, bias=bias)
+        self.scatter = ExpertScatter(E, J, I, bias=bias)
+
+    def forward(self, x: torch.Tensor, Ind: torch.Tensor) -> torch.Tensor:
+        if self.gather.bias is not None or self.scatter.bias is not None:
+            return self.scatter(self.gather(x, Ind), Ind, x.shape[1])
+        return ExpertGatherScatterFunction.apply(x, self.gather.W, self.scatter.W, Ind)

@@ -117,3 +117,27 @@ def test_train_step_uses_the_pair_on_the_float32_configurations(cuda_device):
     launches = ops.launch_count() - n0
     compare_step(got, ref, 1e-5, what="cfg1-T256 fused step")
     assert launches <= 8, launches      # 2 fills + 2 pair kernels + 2 weight gradients (+ their fills)
+
+
+@pytest.mark.parametrize("name,B", [("cfg1-T256", None), ("cfg0", 8), ("cfg2", 1)])
+def test_gather_scatter_module_autograd(cuda_device, name, B):
+    """ExpertGatherScatter (one autograd node; fused kernels where they pay, the two operators otherwise) against the
+    oracle's forward and gradients: float32 fused (cfg1), float32 multi-wave (cfg0 slice), bf16 (cfg2 slice)."""
+    import expertscattergather_b200 as egs
+    w = workloads.WORKLOADS[name]
+    ins = workloads.make_inputs(w, B=B)
+    ref = orc.torch_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    d = to_dev(ins, cuda_device)
+    mod = egs.ExpertGatherScatter(w.E, w.I, w.J).to(cuda_device)
+    mod = mod.to(w.dtype)
+    with torch.no_grad():
+        mod.gather.W.copy_(d["Wg"])
+        mod.scatter.W.copy_(d["Ws"])
+    x = d["X"].clone().requires_grad_(True)
+    ops.reset_status()
+    out = mod(x, d["Ind"])
+    (out.float() * d["G"].float()).sum().backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = {"Out": out.detach().cpu(), "dX": x.grad.cpu(), "dWg": mod.gather.W.grad.cpu(), "dWs": mod.scatter.W.grad.cpu()}
+    compare_step(got, ref, tol_for(w.dtype, "strict"), keys=("Out", "dX", "dWg", "dWs"), what=f"module {name}")

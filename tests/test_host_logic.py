@@ -131,3 +131,16 @@ def test_shard_bounds_cover_the_batch():
             spans = [shard_bounds(B, r, world) for r in range(world)]
             assert spans[0][0] == 0 and spans[-1][1] == B
             assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+
+
+def test_gather_scatter_block_holds_the_two_reference_modules():
+    """The fused block's parameters are those of an ExpertGather and an ExpertScatter, so state dicts interchange."""
+    import expertscattergather_b200 as egs
+    blk = egs.ExpertGatherScatter(3, 16, 8)
+    g, s = egs.ExpertGather(3, 16, 8), egs.ExpertScatter(3, 8, 16)
+    assert sorted(blk.state_dict()) == ["gather.W", "scatter.W"]
+    blk.gather.load_state_dict(g.state_dict())
+    blk.scatter.load_state_dict(s.state_dict())
+    assert tuple(blk.gather.W.shape) == (3, 16, 8) and tuple(blk.scatter.W.shape) == (3, 8, 16)
+    with_bias = egs.ExpertGatherScatter(3, 16, 8, bias=True)
+    assert sorted(with_bias.state_dict()) == ["gather.W", "gather.bias", "scatter.W", "scatter.bias"]
