@@ -284,15 +284,19 @@ def test_no_gathered_intermediate_is_allocated(cuda_device):
 # ragged shapes that reach the large-problem kernel variants (256-row CTA tiles for G, the persistent
 # warp-specialised scatter, direct 16-bit adds) - compared with the generic kernels and the CPU checker
 # ---------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("dtype,precision", [(torch.bfloat16, "strict"), (torch.float32, "tf32")])
-def test_large_variants_on_ragged_shapes(cuda_device, dtype, precision):
+@pytest.mark.parametrize("dtype,precision,T,index", [(torch.bfloat16, "strict", 300, "replace"),
+                                                     (torch.float32, "tf32", 300, "replace"),
+                                                     (torch.bfloat16, "strict", 3000, "distinct")])
+def test_large_variants_on_ragged_shapes(cuda_device, dtype, precision, T, index):
     # M = B*K = 500 rows per expert (not a multiple of 128 or 256), J = 72 (two contraction stages for S, the second
-    # partial), I = 1320 (six 256-wide output tiles for S, the last 40 wide; 21 or 42 contraction stages for G)
-    w = Workload("ragged-large", 5, 300, 80, 100, 1320, 72, dtype, "replace", 808)
+    # partial), I = 1320 (six 256-wide output tiles for S, the last 40 wide; 21 or 42 contraction stages for G).
+    # T = 300 with replacement: dozens of contributions per token (16-bit scatter sums in float32 rows);
+    # T = 3000 distinct: a few per token (16-bit scatter adds directly, as bulk reductions, ragged last tile included).
+    w = Workload("ragged-large", 5, T, 80, 100, 1320, 72, dtype, index, 808)
     ins = workloads.make_inputs(w, integer_valued=True)
-    ins["Ind"][2, 7, 5] = 300          # out of range: skipped and reported
+    ins["Ind"][2, 7, 5] = T            # out of range: skipped and reported
     ins["Ind"][4, 79, 99] = -3
-    ref_ind = ins["Ind"].clamp(0, 299)
+    ref_ind = ins["Ind"].clamp(0, T - 1)
     d = to_dev(ins, cuda_device)
     res = {}
     for path in ("generic", "tensor"):
@@ -321,3 +325,37 @@ def test_large_variants_on_ragged_shapes(cuda_device, dtype, precision):
         assert orc.rel_err(res["tensor"][k], res["generic"][k]) <= tol, (k, orc.rel_err(res["tensor"][k], res["generic"][k]))
     Outref = orc.np_scatter(torch.from_numpy(Yref), ins["Ws"], ref_ind, w.T)
     assert orc.rel_err(res["tensor"]["Out"], Outref) <= tol
+
+
+@pytest.mark.parametrize("dtype,precision", [(torch.bfloat16, "strict"), (torch.float32, "tf32")])
+def test_weight_gradient_two_tile_variant_on_ragged_shapes(cuda_device, dtype, precision):
+    """Operator D where the host picks two 128-feature accumulators per CTA (long contraction, grid covering the SMs):
+    M = B*K = 1100 contraction rows (last stage partial), FG = 1320 features (five full 256-feature tiles and one of
+    40), FD = 72.  Integer-valued inputs make every sum exact in float32, so the tensor-core kernel, the generic
+    kernel and the numpy checker must agree bit for bit, in both output layouts."""
+    w = Workload("ragged-dw", 11, 400, 30, 100, 1320, 72, dtype, "distinct", 909)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    ins["Ind"][3, 4, 5] = 400          # out of range: contributes nothing
+    ref_ind = ins["Ind"].clone()
+    d = to_dev(ins, cuda_device)
+    Ycpu = torch.randint(-3, 4, (w.B, w.E, w.K, w.J), generator=torch.Generator().manual_seed(5)).to(dtype)   # slot rows
+    Y = Ycpu.to(cuda_device)
+    res = {}
+    for path in ("generic", "tensor"):
+        ops.reset_status()
+        dWg = ops.dweight(d["X"], Y, d["Ind"], path=path, precision=precision)                          # [E, I, J]
+        dWs = ops.dweight(d["G"], Y, d["Ind"], out_layout="direct_rows", path=path, precision=precision)  # [E, J, I]
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="outside"):
+            ops.check_status()
+        res[path] = (dWg.cpu(), dWs.cpu())
+    assert torch.equal(res["generic"][0], res["tensor"][0])
+    assert torch.equal(res["generic"][1], res["tensor"][1])
+    # checker: the masked slot adds nothing -> zero its slot row on the checker's side
+    Ymask = Ycpu.clone().float()
+    Ymask[3, 4, 5] = 0
+    ref_ind[3, 4, 5] = 0
+    ref_g = torch.from_numpy(orc.np_dweight(ins["X"], Ymask, ref_ind)).to(dtype)
+    assert torch.equal(res["tensor"][0], ref_g)
+    ref_s = torch.from_numpy(orc.np_dweight(ins["G"], Ymask, ref_ind)).to(dtype).transpose(1, 2).contiguous()
+    assert torch.equal(res["tensor"][1], ref_s)
