@@ -419,11 +419,24 @@ def main():
         h2d = sum(h[k].numel() * h[k].element_size() for h in host for k in ("X", "Ind", "G"))
         d2h = sum(a.numel() * a.element_size() + b.numel() * b.element_size() + 4 for a, b, _ in res_host)
 
+        copy_stream = torch.cuda.Stream(dev)
+
         def e2e_step():
-            for w, h, (g, s), (rg, rs, rl) in zip(passes, host, mods, res_host):
-                X = h["X"].to(dev, non_blocking=True).requires_grad_(True)
-                Ind = h["Ind"].to(dev, non_blocking=True)
-                G = h["G"].to(dev, non_blocking=True)
+            # the host->device copies of all passes are queued on a copy stream at the start of the step (pinned
+            # buffers, one event per pass); the compute stream waits for each pass's event, so the copies of the next
+            # pass run under the kernels of the current one, as an input prefetcher of a training loop would do
+            main = torch.cuda.current_stream(dev)
+            copy_stream.wait_stream(main)
+            staged = []
+            with torch.cuda.stream(copy_stream):
+                for h in host:
+                    t = tuple(h[k].to(dev, non_blocking=True) for k in ("X", "Ind", "G"))
+                    staged.append((t, copy_stream.record_event()))
+            for w, (t, ready), (g, s), (rg, rs, rl) in zip(passes, staged, mods, res_host):
+                main.wait_event(ready)
+                for x in t:
+                    x.record_stream(main)
+                X, Ind, G = t[0].requires_grad_(True), t[1], t[2]
                 g.W.grad = None; s.W.grad = None
                 Out = s(g(X, Ind), Ind, w.T)
                 loss = (Out * G).sum()

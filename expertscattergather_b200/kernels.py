@@ -148,8 +148,9 @@ class ExpertGatherFunction(torch.autograd.Function):
     """``Y[b,e,k,j] = sum_i X[b, Ind[b,e,k], i] * W[e,i,j]`` with X [B,T,I], W [E,I,J], Ind [B,E,K].
 
     Same call signature and return convention as the reference class (``egs/triton_kernels.py:581-608``):
-    ``apply(X, W, Ind, out_type=torch.float32)``; backward returns ``(grad_X, grad_W, None, None)`` and always
-    computes both gradients.
+    ``apply(X, W, Ind, out_type=torch.float32)``; backward returns ``(grad_X, grad_W, None, None)``.  The reference
+    always computes both gradients (``:603-608``); here a gradient autograd does not ask for (``needs_input_grad``: a
+    frozen weight, an input that is data) is not computed.
     """
 
     @staticmethod
@@ -162,7 +163,13 @@ class ExpertGatherFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         X, W, Ind = ctx.saved_tensors
-        grad_X, grad_W = expert_gather_backward_call(X, W, Ind, grad_output, ctx.dtype)
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if need_x and need_w:
+            grad_X, grad_W = expert_gather_backward_call(X, W, Ind, grad_output, ctx.dtype)
+            return grad_X, grad_W, None, None
+        grad_output = grad_output.contiguous()
+        grad_X = ops.gemm_scatter(grad_output, W, Ind, X.shape[1], w_layout="nc") if need_x else None
+        grad_W = ops.dweight(X, grad_output, Ind, out_layout="gathered_rows") if need_w else None
         return grad_X, grad_W, None, None
 
 
@@ -170,7 +177,8 @@ class ExpertScatterFunction(torch.autograd.Function):
     """``Out[b,t,i] = sum_{e,k: Ind[b,e,k]=t} sum_j Y[b,e,k,j] * W[e,j,i]`` with Y [B,E,K,J], W [E,J,I].
 
     Same call signature as the reference class (``egs/triton_kernels.py:610-639``):
-    ``apply(Y, W, Ind, T, out_type=torch.float32)``; backward returns ``(grad_Y, grad_W, None, None, None)``.
+    ``apply(Y, W, Ind, T, out_type=torch.float32)``; backward returns ``(grad_Y, grad_W, None, None, None)``; a
+    gradient autograd does not ask for is not computed (the reference always computes both, ``:634-639``).
     """
 
     @staticmethod
@@ -183,7 +191,13 @@ class ExpertScatterFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_X):
         Y, W, Ind = ctx.saved_tensors
-        grad_Y, grad_W = expert_scatter_backward_call(Y, W, Ind, grad_X, ctx.dtype)
+        need_y, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if need_y and need_w:
+            grad_Y, grad_W = expert_scatter_backward_call(Y, W, Ind, grad_X, ctx.dtype)
+            return grad_Y, grad_W, None, None, None
+        grad_X = grad_X.contiguous()
+        grad_Y = ops.gather_gemm(grad_X, W, Ind, w_layout="nc") if need_y else None
+        grad_W = ops.dweight(grad_X, Y, Ind, out_layout="direct_rows") if need_w else None
         return grad_Y, grad_W, None, None, None
 
 
@@ -196,7 +210,7 @@ class ExpertGatherScatterFunction(torch.autograd.Function):
     kernel (Y is written once, for the backward pass, and consumed from shared memory) and so is dY -> dX of the
     backward pass; otherwise each pass runs the two separate operators.  The weight gradients are the same two
     contractions as in ``ExpertGatherFunction`` / ``ExpertScatterFunction`` and run next to dY -> dX on the helper
-    stream.  backward returns ``(grad_X, grad_W_g, grad_W_s, None)`` and always computes all three.
+    stream.  backward returns ``(grad_X, grad_W_g, grad_W_s, None)``; gradients autograd does not ask for are skipped.
     """
 
     @staticmethod
@@ -214,15 +228,19 @@ class ExpertGatherScatterFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         X, Wg, Ws, Ind, Y = ctx.saved_tensors
+        need_x, need_wg, need_ws = ctx.needs_input_grad[:3]
         grad_out = grad_out.contiguous()
-        grad_Ws = _weight_grad_on_side_stream(grad_out, Y, Ind, "direct_rows")       # needs only dOut and Y
-        if ctx.fused:
+        grad_X = grad_Wg = grad_Ws = dY = None
+        if need_ws:
+            grad_Ws = _weight_grad_on_side_stream(grad_out, Y, Ind, "direct_rows")   # needs only dOut and Y
+        if need_x and ctx.fused:
             dY, grad_X = ops.gather_scatter_pair(grad_out, Ws, Wg, Ind, w_layout="nc")
-        else:
+        elif need_x or need_wg:
             dY = ops.gather_gemm(grad_out, Ws, Ind, w_layout="nc")
-            grad_X = None
-        grad_Wg = _weight_grad_on_side_stream(X, dY, Ind, "gathered_rows")
-        if grad_X is None:
+        if need_wg:
+            grad_Wg = _weight_grad_on_side_stream(X, dY, Ind, "gathered_rows")
+        if need_x and grad_X is None:
             grad_X = ops.gemm_scatter(dY, Wg, Ind, X.shape[1], w_layout="nc")
-        _join_side(grad_X)
+        if need_ws or need_wg:
+            _join_side(grad_out)
         return grad_X, grad_Wg, grad_Ws, None

@@ -359,3 +359,34 @@ def test_weight_gradient_two_tile_variant_on_ragged_shapes(cuda_device, dtype, p
     assert torch.equal(res["tensor"][0], ref_g)
     ref_s = torch.from_numpy(orc.np_dweight(ins["G"], Ymask, ref_ind)).to(dtype).transpose(1, 2).contiguous()
     assert torch.equal(res["tensor"][1], ref_s)
+
+
+def test_gradients_nobody_asked_for_are_not_computed(cuda_device):
+    """needs_input_grad pruning: with a frozen weight or a data input the corresponding kernel is not launched, and
+    the gradient that is asked for is unchanged."""
+    w = Workload("prune", 3, 64, 4, 16, 64, 32, torch.float32, "distinct", 21)
+    ins = workloads.make_inputs(w)
+    ref = orc.torch_step(ins["X"], ins["Wg"], ins["Ws"], ins["Ind"], ins["G"])
+    d = to_dev(ins, cuda_device)
+
+    def run(x_grad, w_grad):
+        g = egs.ExpertGather(w.E, w.I, w.J).to(cuda_device)
+        s = egs.ExpertScatter(w.E, w.J, w.I).to(cuda_device)
+        with torch.no_grad():
+            g.W.copy_(d["Wg"]); s.W.copy_(d["Ws"])
+        g.W.requires_grad_(w_grad); s.W.requires_grad_(w_grad)
+        x = d["X"].clone().requires_grad_(x_grad)
+        out = s(g(x, d["Ind"]), d["Ind"], w.T)
+        n0 = ops.launch_count()
+        (out * d["G"]).sum().backward()
+        torch.cuda.synchronize()
+        return ops.launch_count() - n0, x.grad, g.W.grad, s.W.grad
+
+    n_all, dx, dwg, dws = run(True, True)
+    n_x, dx_only, none_g, none_s = run(True, False)
+    n_w, none_x, dwg_only, dws_only = run(False, True)
+    assert none_g is None and none_s is None and none_x is None
+    assert n_x < n_all and n_w < n_all
+    for a, b in ((dx_only, dx), (dwg_only, dwg), (dws_only, dws)):      # float32 atomics: equal up to summation order
+        assert orc.rel_err(a.cpu(), b.cpu()) <= 1e-6
+    assert orc.rel_err(dx.cpu(), ref["dX"]) <= 1e-5 and orc.rel_err(dwg.cpu(), ref["dWg"]) <= 1e-5
