@@ -26,6 +26,8 @@ SHAPES = [
     (5, 300, 3, 60, 100, 32),        # contraction not a multiple of 32, N2 = 100 (not a multiple of 16)
     (2, 64, 2, 40, 36, 64),          # two stages of contraction, one of them partial
     (9, 40, 4, 33, 64, 32),          # B*K = 297: three row tiles, the last one partial
+    (2, 64, 2, 40, 32, 96),          # one stage in phase 1, three in phase 2 on a 2-stage ring; 24 chunks per weight row
+    (3, 80, 3, 50, 256, 128),        # TF32 only (strict tiles do not fit): eight + four stages
 ]
 
 
