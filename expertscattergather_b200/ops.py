@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "fused_pair_preferred", "dweight", "fill_zero", "side_stream", "set_precision", "get_precision", "set_path", "get_path",
+__all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "fused_pair_preferred", "dweight", "fill_zero", "side_stream", "fill_stream", "set_precision", "get_precision", "set_path", "get_path",
            "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
@@ -109,6 +109,7 @@ def check_status(device=None) -> None:
 
 
 _side_streams: dict[int, "torch.cuda.Stream"] = {}
+_fill_streams: dict[int, "torch.cuda.Stream"] = {}
 
 
 def side_stream(device) -> "torch.cuda.Stream":
@@ -121,6 +122,19 @@ def side_stream(device) -> "torch.cuda.Stream":
     if st is None:
         st = torch.cuda.Stream(torch.device("cuda", idx))
         _side_streams[idx] = st
+    return st
+
+
+def fill_stream(device) -> "torch.cuda.Stream":
+    """A second per-device helper stream, for the zero fills of a step's outputs alone: kept apart from
+    :func:`side_stream` so that the fills of the next step are not ordered behind the weight-gradient kernels of the
+    current one."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _fill_streams.get(idx)
+    if st is None:
+        st = torch.cuda.Stream(torch.device("cuda", idx))
+        _fill_streams[idx] = st
     return st
 
 

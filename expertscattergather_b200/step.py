@@ -71,20 +71,22 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     fused = fused_pairs and prefill and takes_fused_pairs(X, Wg, Ind)
     Out = dX = None
     if prefill:
-        # The two outputs are allocated and zero-filled on the side stream, from its own memory pool: nothing ties
-        # the fills to work already queued on the main stream (the tail of the previous step), so they run under
-        # it.  Inside a stream capture the side stream first has to join the capture through the main stream.
-        if _is_capturing(main) and not _is_capturing(side):
-            side.wait_stream(main)
-        with torch.cuda.stream(side):
+        # The two outputs are allocated and zero-filled on a stream of their own, from its memory pool: nothing ties
+        # the fills to work already queued on the main stream or to the weight-gradient kernels on the side stream
+        # (the tail of the previous step), so they run under it.  Inside a stream capture the fill stream first has
+        # to join the capture through the main stream.
+        fills = ops.fill_stream(dev)
+        if _is_capturing(main) and not _is_capturing(fills):
+            fills.wait_stream(main)
+        with torch.cuda.stream(fills):
             Out = torch.empty((X.shape[0], T, Ws.shape[2]), device=dev, dtype=X.dtype)
             dX = torch.empty_like(X, memory_format=torch.contiguous_format)
             Out.record_stream(main)
             dX.record_stream(main)
             ops.fill_zero(Out)
-            out_filled = side.record_event()
+            out_filled = fills.record_event()
             ops.fill_zero(dX)
-        fills_done = side.record_event()
+        fills_done = fills.record_event()
     if prefill and fused:
         # float32 shapes the fused pair kernel takes: two kernels on the critical chain instead of four
         main.wait_event(out_filled)
