@@ -477,7 +477,7 @@ def main():
                        "routed_tokens_per_step": tokens_per_step, "parallelism": f"dp{world} (batch-sharded, dW all-reduce)",
                        "l2": "flush buffer written between steps" if flush_buf is not None else "inputs larger than L2",
                        "cuda_graph": bool(graph is not None), "precision": ops.get_precision(),
-                       "streams": "zero fills and weight gradients on a side stream next to the G->S->dY->dX chain"},
+                       "streams": "output zero fills on a fill stream, weight gradients on a side stream, next to the G->S->dY->dX chain"},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
             "roofline": roof,

@@ -22,6 +22,29 @@ def _is_capturing(stream: "torch.cuda.Stream") -> bool:
         return bool(torch.cuda.is_current_stream_capturing())
 
 
+def _prefilled_outputs(X: torch.Tensor, T: int, n_out: int, main: "torch.cuda.Stream"):
+    """Allocates Out [B,T,n_out] and dX (like X) and zero-fills them on the fill stream; returns the two tensors, an
+    event for "Out is filled" and one for "both are filled".
+
+    The tensors come from the fill stream's own memory pool: nothing ties the fills to work already queued on the
+    main stream or to the weight-gradient kernels on the side stream (the tail of the previous step), so they run
+    under it.  The scatters then add into the zeros.  Inside a stream capture the fill stream first joins the capture
+    through the main stream."""
+    dev = X.device
+    fills = ops.fill_stream(dev)
+    if _is_capturing(main) and not _is_capturing(fills):
+        fills.wait_stream(main)
+    with torch.cuda.stream(fills):
+        Out = torch.empty((X.shape[0], T, n_out), device=dev, dtype=X.dtype)
+        dX = torch.empty_like(X, memory_format=torch.contiguous_format)
+        Out.record_stream(main)
+        dX.record_stream(main)
+        ops.fill_zero(Out)
+        out_filled = fills.record_event()
+        ops.fill_zero(dX)
+    return Out, dX, out_filled, fills.record_event()
+
+
 def takes_fused_pairs(X: torch.Tensor, Wg: torch.Tensor, Ind: torch.Tensor) -> bool:
     """Whether :func:`train_step` runs G -> S and dY -> dX as one fused kernel each for these tensors."""
     return ops.fused_pair_preferred(X, Wg, Ind)
@@ -35,25 +58,34 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     Returns Y, Out, dY, dX, dWg, dWs.  Equivalent to
     ``Y = ExpertGather(X, Ind); Out = ExpertScatter(Y, Ind, T); (Out*G).sum().backward()``.
 
-    With ``overlap`` the work that is off the critical chain G -> S -> dY -> dX runs on a side stream: the zero
-    fills of Out and dX (float32 tensors; 16-bit outputs are initialised by the scatter's own planning step) and
-    the two weight-gradient kernels, each started as soon as its inputs exist.  With ``on_weight_grad`` (the
-    data-parallel case) everything stays on one stream in an order that puts both weight gradients, and with them
-    the start of their reductions, before the last scatter.  With ``fused_pairs`` float32 shapes that the fused
+    With ``overlap`` the work that is off the critical chain G -> S -> dY -> dX runs on helper streams: the zero fills
+    of float32 Out and dX on a fill stream (the scatters then add into the zeros; 16-bit outputs are initialised by
+    the scatter's own planning step), the two weight-gradient kernels on a side stream, each started as soon as its
+    inputs exist.  With ``on_weight_grad`` (the data-parallel case) the operators
+    stay on one stream in an order that puts both weight gradients, and with them the start of their reductions,
+    before the last scatter; only the fills run beside them.  With ``fused_pairs`` float32 shapes that the fused
     pair kernel takes run G -> S and dY -> dX as one kernel each.
     """
     T = X.shape[1]
     if on_weight_grad is not None:
         # data-parallel order: both weight gradients come before the long dX scatter, so that the reductions the
         # callback starts (dW_s first, then dW_g) run behind the kernels that are still to come
+        main = torch.cuda.current_stream(X.device)
+        Out = dX = None
+        if X.dtype == torch.float32:
+            Out, dX, out_filled, fills_done = _prefilled_outputs(X, T, Ws.shape[2], main)
         Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")
-        Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn")
+        if Out is not None:
+            main.wait_event(out_filled)
+        Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn", out=Out)
         dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")
         dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")
         on_weight_grad("Ws", dWs)
         dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
         on_weight_grad("Wg", dWg)
-        dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc")
+        if dX is not None:
+            main.wait_event(fills_done)
+        dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc", out=dX)
         return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
     if not overlap:
         Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                 # gather forward
@@ -67,27 +99,14 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     dev = X.device
     main = torch.cuda.current_stream(dev)
     side = ops.side_stream(dev)
+    # float32 outputs are zero-filled ahead of time on the fill stream; 16-bit outputs are initialised by the scatter's
+    # own planning step (prefilling them measured slower where the scatter sums in float32 rows)
     prefill = X.dtype == torch.float32
     fused = fused_pairs and prefill and takes_fused_pairs(X, Wg, Ind)
     Out = dX = None
     if prefill:
-        # The two outputs are allocated and zero-filled on a stream of their own, from its memory pool: nothing ties
-        # the fills to work already queued on the main stream or to the weight-gradient kernels on the side stream
-        # (the tail of the previous step), so they run under it.  Inside a stream capture the fill stream first has
-        # to join the capture through the main stream.
-        fills = ops.fill_stream(dev)
-        if _is_capturing(main) and not _is_capturing(fills):
-            fills.wait_stream(main)
-        with torch.cuda.stream(fills):
-            Out = torch.empty((X.shape[0], T, Ws.shape[2]), device=dev, dtype=X.dtype)
-            dX = torch.empty_like(X, memory_format=torch.contiguous_format)
-            Out.record_stream(main)
-            dX.record_stream(main)
-            ops.fill_zero(Out)
-            out_filled = fills.record_event()
-            ops.fill_zero(dX)
-        fills_done = fills.record_event()
-    if prefill and fused:
+        Out, dX, out_filled, fills_done = _prefilled_outputs(X, T, Ws.shape[2], main)
+    if fused:
         # float32 shapes the fused pair kernel takes: two kernels on the critical chain instead of four
         main.wait_event(out_filled)
         Y, Out = ops.gather_scatter_pair(X, Wg, Ws, Ind, w_layout="cn", out=Out)      # gather + scatter forward
@@ -107,7 +126,7 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
     Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")                     # gather forward
     if prefill:
-        main.wait_event(fills_done)
+        main.wait_event(out_filled)
     Out = ops.gemm_scatter(Y, Ws, Ind, T, w_layout="cn", out=Out)      # scatter forward (adds into zeros)
     fwd_done = main.record_event()
     with torch.cuda.stream(side):                                      # scatter backward: dW_s, next to dY
@@ -120,6 +139,8 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         side.wait_event(dy_ready)
         dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
         dWg.record_stream(main)
+    if prefill:
+        main.wait_event(fills_done)
     dX = ops.gemm_scatter(dY, Wg, Ind, T, w_layout="nc", out=dX)       # gather backward: dX
     main.wait_stream(side)                                             # join
     return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
