@@ -240,9 +240,12 @@ size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype) {
   return static_cast<size_t>(E) * FG * FD * sizeof(float);
 }
 
-int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
-                int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision, int path,
-                void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+// out_is_zero: the caller guarantees that a float32 `out` holds zeros on entry, so the fill before a split
+// contraction (which accumulates straight into `out`) is skipped.
+static int dweight_impl(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
+                        int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision,
+                        int path, void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream,
+                        bool out_is_zero) {
   egs_dims d{B, T, E, K, FG, FD};
   if (int rc = check_dims(&d)) return rc;
   if (!valid_dtype(dtype) || !valid_index(index_dtype) ||
@@ -256,6 +259,7 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, 
   if (!out) return EGS_ERR_INVALID_ARGUMENT;
   const int es = elem_size(dtype);
   if (B * K == 0) {   // nothing to sum: the gradient is zero
+    if (out_is_zero && dtype == EGS_F32) return EGS_OK;
     cudaError_t err = launch_fill_zero(out, n_out * es, st);
     return err == cudaSuccess ? EGS_OK : fail_cuda(err, "fill_zero");
   }
@@ -298,8 +302,10 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, 
       if (!workspace || workspace_bytes < n_out * sizeof(float)) return EGS_ERR_WORKSPACE;
       p.acc = static_cast<float*>(workspace);
     }
-    err = launch_fill_zero(p.acc, n_out * sizeof(float), st);
-    if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+    if (!(out_is_zero && dtype == EGS_F32)) {
+      err = launch_fill_zero(p.acc, n_out * sizeof(float), st);
+      if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+    }
   }
   err = tensor ? launch_tensor_dweight(p, dtype, precision, smem, st) : launch_generic_dweight(p, dtype, st);
   if (err != cudaSuccess) return fail_cuda(err, "dweight launch");
@@ -318,6 +324,20 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, 
 #define EGS_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)          /* 16 MiB, held by every device that loads the library */
 static __device__ __align__(256) float g_static_dw_scratch[EGS_STATIC_SCRATCH_FLOATS];
 static float* g_static_dw_scratch_addr[64] = {};             /* per device ordinal, filled on first use */
+
+int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
+                int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision, int path,
+                void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  return dweight_impl(Xsrc, Ysrc, Ind, out, B, T, E, K, FG, FD, out_layout, dtype, index_dtype, precision, path, workspace,
+                      workspace_bytes, status_word, cuda_stream, false);
+}
+
+int egs_dweight_prezeroed(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
+                          int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision,
+                          int path, void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  return dweight_impl(Xsrc, Ysrc, Ind, out, B, T, E, K, FG, FD, out_layout, dtype, index_dtype, precision, path, workspace,
+                      workspace_bytes, status_word, cuda_stream, true);
+}
 
 int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T,
                                int64_t E, int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype,

@@ -313,9 +313,11 @@ def gather_scatter_pair(Src, W1, W2, Ind, *, w_layout="cn", out=None, precision=
     return Mid, out
 
 
-def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path=None):
+def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path=None, zeroed_out=None):
     """Operator D: ``P[e,f,g] = sum_{b,k} Xsrc[b, Ind[b,e,k], f] * Ysrc[b,e,k,g]``.
-    'gathered_rows' returns P [E,FG,FD]; 'direct_rows' returns P^T [E,FD,FG]."""
+    'gathered_rows' returns P [E,FG,FD]; 'direct_rows' returns P^T [E,FD,FG].
+    ``zeroed_out``: an output tensor the caller has already zero-filled (float32 only) - the library then skips its
+    own fill, which lets a caller issue the fill early, off the critical path."""
     lib = _lib.load()
     if Xsrc.dim() != 3 or Ysrc.dim() != 4 or Ind.dim() != 3:
         raise ValueError("expected Xsrc[B,T,FG], Ysrc[B,E,K,FD], Ind[B,E,K]")
@@ -337,10 +339,17 @@ def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path
     Ic, it = _index_tensor(Ind)
     prec, pth = _enums(precision, path)
     with torch.cuda.device(dev):
-        out = torch.empty(shape, device=dev, dtype=Xsrc.dtype)
+        fn = lib.egs_dweight
+        if zeroed_out is not None:
+            if (tuple(zeroed_out.shape) != shape or zeroed_out.dtype != torch.float32 or Xsrc.dtype != torch.float32
+                    or not zeroed_out.is_contiguous()):
+                raise ValueError("zeroed_out must be a contiguous float32 tensor of the output's shape")
+            out, fn = zeroed_out, lib.egs_dweight_prezeroed
+        else:
+            out = torch.empty(shape, device=dev, dtype=Xsrc.dtype)
         ws_bytes = int(lib.egs_dw_workspace_bytes(E, FG, FD, dt))
         ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if ws_bytes else None
-        rc = lib.egs_dweight(Xc.data_ptr(), Yc.data_ptr(), Ic.data_ptr(), out.data_ptr(), B, T, E, K, FG, FD, ol, dt, it,
+        rc = fn(Xc.data_ptr(), Yc.data_ptr(), Ic.data_ptr(), out.data_ptr(), B, T, E, K, FG, FD, ol, dt, it,
                              prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
                              _status_word(dev).data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "egs_dweight")

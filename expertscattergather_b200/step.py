@@ -22,9 +22,9 @@ def _is_capturing(stream: "torch.cuda.Stream") -> bool:
         return bool(torch.cuda.is_current_stream_capturing())
 
 
-def _prefilled_outputs(X: torch.Tensor, T: int, n_out: int, main: "torch.cuda.Stream"):
+def _prefilled_outputs(X: torch.Tensor, T: int, n_out: int, main: "torch.cuda.Stream", dw_shapes=()):
     """Allocates Out [B,T,n_out] and dX (like X) and zero-fills them on the fill stream; returns the two tensors, an
-    event for "Out is filled" and one for "both are filled".
+    event for "Out is filled", one for "everything is filled", and zero-filled tensors of the shapes in ``dw_shapes``.
 
     The tensors come from the fill stream's own memory pool: nothing ties the fills to work already queued on the
     main stream or to the weight-gradient kernels on the side stream (the tail of the previous step), so they run
@@ -42,7 +42,11 @@ def _prefilled_outputs(X: torch.Tensor, T: int, n_out: int, main: "torch.cuda.St
         ops.fill_zero(Out)
         out_filled = fills.record_event()
         ops.fill_zero(dX)
-    return Out, dX, out_filled, fills.record_event()
+        # the weight gradients accumulate into zeros as well: filled here, long before their kernels are due
+        dW0 = [ops.fill_zero(torch.empty(shape, device=dev, dtype=X.dtype)) for shape in dw_shapes]
+        for t in dW0:
+            t.record_stream(ops.side_stream(dev))
+    return Out, dX, out_filled, fills.record_event(), dW0
 
 
 def takes_fused_pairs(X: torch.Tensor, Wg: torch.Tensor, Ind: torch.Tensor) -> bool:
@@ -73,7 +77,7 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         main = torch.cuda.current_stream(X.device)
         Out = dX = None
         if X.dtype == torch.float32:
-            Out, dX, out_filled, fills_done = _prefilled_outputs(X, T, Ws.shape[2], main)
+            Out, dX, out_filled, fills_done, _ = _prefilled_outputs(X, T, Ws.shape[2], main)
         Y = ops.gather_gemm(X, Wg, Ind, w_layout="cn")
         if Out is not None:
             main.wait_event(out_filled)
@@ -104,8 +108,10 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     prefill = X.dtype == torch.float32
     fused = fused_pairs and prefill and takes_fused_pairs(X, Wg, Ind)
     Out = dX = None
+    dWs0 = dWg0 = None
     if prefill:
-        Out, dX, out_filled, fills_done = _prefilled_outputs(X, T, Ws.shape[2], main)
+        Out, dX, out_filled, fills_done, (dWs0, dWg0) = _prefilled_outputs(
+            X, T, Ws.shape[2], main, dw_shapes=(tuple(Ws.shape), tuple(Wg.shape)))
     if fused:
         # float32 shapes the fused pair kernel takes: two kernels on the critical chain instead of four
         main.wait_event(out_filled)
@@ -113,14 +119,15 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
         fwd_done = main.record_event()
         with torch.cuda.stream(side):
             side.wait_event(fwd_done)
-            dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")                  # scatter backward: dW_s
+            side.wait_event(fills_done)
+            dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows", zeroed_out=dWs0)  # scatter backward: dW_s
             dWs.record_stream(main)
         main.wait_event(fills_done)
         dY, dX = ops.gather_scatter_pair(G, Ws, Wg, Ind, w_layout="nc", out=dX)       # dY and dX
         dy_ready = main.record_event()
         with torch.cuda.stream(side):
             side.wait_event(dy_ready)
-            dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")               # gather backward: dW_g
+            dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows", zeroed_out=dWg0)   # gather backward: dW_g
             dWg.record_stream(main)
         main.wait_stream(side)
         return {"Y": Y, "Out": Out, "dY": dY, "dX": dX, "dWg": dWg, "dWs": dWs}
@@ -131,13 +138,15 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     fwd_done = main.record_event()
     with torch.cuda.stream(side):                                      # scatter backward: dW_s, next to dY
         side.wait_event(fwd_done)                                      # the backward pass starts after the forward
-        dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows")
+        if prefill:
+            side.wait_event(fills_done)
+        dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows", zeroed_out=dWs0)
         dWs.record_stream(main)
     dY = ops.gather_gemm(G, Ws, Ind, w_layout="nc")                    # scatter backward: dY
     dy_ready = main.record_event()
     with torch.cuda.stream(side):                                      # gather backward: dW_g, next to dX
         side.wait_event(dy_ready)
-        dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows")
+        dWg = ops.dweight(X, dY, Ind, out_layout="gathered_rows", zeroed_out=dWg0)
         dWg.record_stream(main)
     if prefill:
         main.wait_event(fills_done)

@@ -116,6 +116,15 @@ int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out,
                 int out_layout, int dtype, int index_dtype, int precision, int path,
                 void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
 
+/* egs_dweight for a caller that has already zero-filled a float32 `out` (the reference's wrappers do exactly that before
+ * their accumulating kernel: torch.zeros_like, egs/triton_kernels.py:409 and :492): the library's own fill before a split
+ * contraction is skipped, so the fill can be issued early, off the critical path.  For 16-bit tensors the promise is
+ * ignored (they accumulate in the workspace) and the call equals egs_dweight. */
+int egs_dweight_prezeroed(const void* Xsrc, const void* Ysrc, const void* Ind, void* out,
+                          int64_t B, int64_t T, int64_t E, int64_t K, int64_t FG, int64_t FD,
+                          int out_layout, int dtype, int index_dtype, int precision, int path,
+                          void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
+
 /* Scratch bytes egs_dweight needs for these sizes (0 for float32 tensors).  No reference counterpart:
  * the reference accumulates dW with atomics directly in the output dtype (egs/triton_kernels.py:356). */
 size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype);

@@ -390,3 +390,20 @@ def test_gradients_nobody_asked_for_are_not_computed(cuda_device):
     for a, b in ((dx_only, dx), (dwg_only, dwg), (dws_only, dws)):      # float32 atomics: equal up to summation order
         assert orc.rel_err(a.cpu(), b.cpu()) <= 1e-6
     assert orc.rel_err(dx.cpu(), ref["dX"]) <= 1e-5 and orc.rel_err(dwg.cpu(), ref["dWg"]) <= 1e-5
+
+
+def test_weight_gradient_into_a_prezeroed_output(cuda_device):
+    """egs_dweight_prezeroed: the caller's zero-filled float32 output is accumulated into without a fill of the
+    library's own; the result equals the plain call's, and 16-bit tensors are refused (they sum in scratch)."""
+    w = Workload("prezero", 4, 96, 6, 24, 64, 32, torch.float32, "distinct", 31)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    d = to_dev(ins, cuda_device)
+    Y = ops.gather_gemm(d["X"], d["Wg"], d["Ind"])
+    plain = ops.dweight(d["X"], Y, d["Ind"])
+    buf = torch.zeros_like(plain)
+    n0 = ops.launch_count()
+    got = ops.dweight(d["X"], Y, d["Ind"], zeroed_out=buf)
+    assert ops.launch_count() - n0 == 1          # the contraction kernel alone
+    assert got is buf and torch.equal(got, plain)
+    with pytest.raises(ValueError, match="float32"):
+        ops.dweight(d["X"].bfloat16(), Y.bfloat16(), d["Ind"], zeroed_out=buf)
