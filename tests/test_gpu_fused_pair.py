@@ -143,3 +143,14 @@ def test_gather_scatter_module_autograd(cuda_device, name, B):
     ops.check_status()
     got = {"Out": out.detach().cpu(), "dX": x.grad.cpu(), "dWg": mod.gather.W.grad.cpu(), "dWs": mod.scatter.W.grad.cpu()}
     compare_step(got, ref, tol_for(w.dtype, "strict"), keys=("Out", "dX", "dWg", "dWs"), what=f"module {name}")
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int16, torch.int32, torch.uint8])
+def test_pair_index_dtypes(cuda_device, idx_dtype):
+    """Ind in every integer width the operators take (narrower ones are widened by the host like the others)."""
+    w = Workload("pair-idx", 3, 100, 4, 20, 64, 32, torch.float32, "distinct", 13)
+    ins = workloads.make_inputs(w, integer_valued=True)
+    d = to_dev(ins, cuda_device)
+    Y64, Out64 = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"])
+    Y, Out = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"].to(idx_dtype))
+    assert torch.equal(Y, Y64) and torch.equal(Out, Out64)
