@@ -24,7 +24,7 @@ STATUS_INDEX_OUT_OF_RANGE, STATUS_PIPELINE_TIMEOUT, STATUS_INTERNAL = 1, 2, 4
 EXPORTS = (
     "egs_version", "egs_status_string", "egs_last_cuda_error", "egs_gather_gemm", "egs_gemm_scatter",
     "egs_dweight", "egs_dweight_static_scratch", "egs_static_scratch_max_elements", "egs_dw_workspace_bytes", "egs_scatter_workspace_bytes", "egs_tensor_path_eligible", "egs_fill_zero", "egs_launch_count",
-    "egs_gather_scatter_pair", "egs_fused_pair_eligible", "egs_dweight_prezeroed",
+    "egs_gather_scatter_pair", "egs_fused_pair_eligible", "egs_dweight_prezeroed", "egs_selftest_wait_timeout",
 )
 
 
@@ -52,6 +52,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_scatter_workspace_bytes.argtypes = [i64, i64, i64, i]
     lib.egs_dweight.restype = i
     lib.egs_dweight.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i, i, i, i, i, vp, sz, vp, vp]
+    lib.egs_selftest_wait_timeout.restype = i
+    lib.egs_selftest_wait_timeout.argtypes = [vp, vp, i64, vp]
     lib.egs_dweight_prezeroed.restype = i
     lib.egs_dweight_prezeroed.argtypes = lib.egs_dweight.argtypes
     lib.egs_dweight_static_scratch.restype = i

@@ -187,6 +187,13 @@ int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, c
                      workspace_bytes, status_word, cuda_stream);
 }
 
+int egs_selftest_wait_timeout(int32_t* status_word, int* out2, int64_t limit_cycles, void* cuda_stream) {
+  if (!status_word || !out2 || limit_cycles < 1 || limit_cycles > (1LL << 31)) return EGS_ERR_INVALID_ARGUMENT;
+  if (!device_is_sm100()) return EGS_ERR_UNSUPPORTED;
+  cudaError_t err = launch_wait_timeout_selftest(status_word, out2, limit_cycles, static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "selftest launch");
+}
+
 int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision) {
   if (dtype != EGS_F32 || C1 > (1 << 24) || N1 > (1 << 24) || N2 > (1 << 24) || C1 < 0 || N1 < 0 || N2 < 0) return 0;
   if (!device_is_sm100()) return 0;

@@ -124,6 +124,9 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
 size_t configure_tensor_fused_pair(FusedParams& p, int precision);
 cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t smem_bytes, cudaStream_t st);
 
+// Bounded-wait self-test (see the kernel): out = two ints on the device.
+cudaError_t launch_wait_timeout_selftest(int32_t* status, int* out, long long limit_cycles, cudaStream_t st);
+
 void count_launch(int n = 1);
 
 }  // namespace egs

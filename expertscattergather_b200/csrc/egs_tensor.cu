@@ -112,7 +112,7 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the CTA is aborting (this or another thread ran out of time).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          int32_t* status) {
+                                          int32_t* status, long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -120,7 +120,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity)) return true;
     if (((++spins) & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1u;
         if (status) atomicOr(status, EGS_STATUS_PIPELINE_TIMEOUT);
         return false;
@@ -1981,6 +1981,27 @@ __global__ void __launch_bounds__(17 * 32, 1) tensor_fused_pair_kernel(FusedPara
 }
 
 // ------------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nobody ever completes, with a short limit.
+// The wait must give up, raise the abort flag and EGS_STATUS_PIPELINE_TIMEOUT, and the kernel must return normally
+// (the context stays usable).  out[0] = 1 if the wait returned false, out[1] = the abort flag afterwards.
+// ------------------------------------------------------------------------------------------------
+__global__ void wait_timeout_selftest_kernel(int32_t* status, int* out, long long limit_cycles) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    abort_flag = 0u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, status, limit_cycles);
+    out[0] = ok ? 0 : 1;
+    out[1] = static_cast<int>(abort_flag);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host side: tile / stage selection and launches
 // ------------------------------------------------------------------------------------------------
 constexpr size_t kSmemPerSm = 228 * 1024;
@@ -2243,6 +2264,12 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
 #undef EGS_LAUNCH
 #undef EGS_LAUNCH_D
   if (err != cudaSuccess) return err;
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_timeout_selftest(int32_t* status, int* out, long long limit_cycles, cudaStream_t st) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(status, out, limit_cycles);
   count_launch();
   return cudaGetLastError();
 }

@@ -173,6 +173,13 @@ int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, con
  * <= 256, N2 within one tile (128 strict / 256 TF32), 16-byte row pitches, and the tiles fit in shared memory. */
 int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision);
 
+/* Self-test of the kernels' bounded waits (no reference counterpart).  Launches one CTA that waits, with a limit of
+ * limit_cycles SM clocks (at most 2^31, about a second), on a barrier nobody completes.  The wait gives up, the kernel
+ * returns normally, EGS_STATUS_PIPELINE_TIMEOUT is set in *status_word, and out2 (two ints on the device) receives
+ * {1 if the wait reported failure, the CTA's abort flag}.  This is the mechanism every pipeline wait in the library uses;
+ * the test shows that a wait that can never be satisfied costs its limit, not the GPU. */
+int egs_selftest_wait_timeout(int32_t* status_word, int* out2, int64_t limit_cycles, void* cuda_stream);
+
 /* 1 if EGS_PATH_AUTO would take the tcgen05 tensor-core kernels for this operator and shape, else 0.
  * op: 0 = G, 1 = S, 2 = D (for D pass C=FG, N=FD).  No reference counterpart (diagnostic). */
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers,
