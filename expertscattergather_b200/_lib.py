@@ -69,7 +69,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_launch_count.restype = i64
     lib.egs_launch_count.argtypes = []
     lib.egs_gather_scatter_pair.restype = i
-    lib.egs_gather_scatter_pair.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i, i, i, i, i, vp, vp]
+    lib.egs_gather_scatter_pair.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i, i, i, i, i, vp, sz, vp, vp]
     lib.egs_fused_pair_eligible.restype = i
     lib.egs_fused_pair_eligible.argtypes = [i64, i64, i64, i, i, i]
 

@@ -4,9 +4,36 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cuda.h>   // types of the driver API only (CUtensorMap); the entry point is looked up at run time, libcuda is not linked
+
 #include "egs_internal.cuh"
 
 namespace egs {
+
+bool encode_tensor_map_16bit(TensorMap3* out, const void* base, const unsigned long long dims[3], const unsigned box[3]) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = []() -> EncodeFn {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  static_assert(sizeof(TensorMap3) == sizeof(CUtensorMap), "tensor map size");
+  if (!encode || !out || !base) return false;
+  const cuuint64_t gdim[3] = {dims[0], dims[1], dims[2]};
+  const cuuint64_t gstride[2] = {dims[0] * 2ull, dims[0] * dims[1] * 2ull};      // bytes, dimensions 1 and 2
+  const cuuint32_t bdim[3] = {box[0], box[1], box[2]};
+  const cuuint32_t estride[3] = {1u, 1u, 1u};
+  // CU_TENSOR_MAP_DATA_TYPE_UINT16: the loads only move bits, so one map type serves bf16 and fp16
+  const CUresult rc = encode(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT16, 3u, const_cast<void*>(base), gdim,
+                             gstride, bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
 
 static std::atomic<long long> g_launches{0};
 static thread_local char g_cuda_error[256] = "";
@@ -136,10 +163,6 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     const double act_bytes = static_cast<double>(d.B) * d.T * (scatter ? d.N * 4.0 : d.C * static_cast<double>(elem_size(dtype)));
     const double w_bytes = static_cast<double>(d.E) * d.C * d.N * elem_size(dtype);
     p.expert_fastest = (act_bytes > 96e6 && w_bytes < 64e6 && (d.B * d.K + 127) / 128 <= 65535) ? 1 : 0;
-    {
-      static const char* order_env = getenv("EGS_B200_EXPERT_FASTEST");   // tuning aid: force the grid order
-      if (order_env && (d.B * d.K + 127) / 128 <= 65535) p.expert_fastest = atoi(order_env) ? 1 : 0;
-    }
     const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
     err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
   } else {
@@ -195,17 +218,18 @@ int egs_selftest_wait_timeout(int32_t* status_word, int* out2, int64_t limit_cyc
 }
 
 int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision) {
-  if (dtype != EGS_F32 || C1 > (1 << 24) || N1 > (1 << 24) || N2 > (1 << 24) || C1 < 0 || N1 < 0 || N2 < 0) return 0;
+  if (!valid_dtype(dtype) || C1 > (1 << 24) || N1 > (1 << 24) || N2 > (1 << 24) || C1 < 0 || N1 < 0 || N2 < 0) return 0;
   if (!device_is_sm100()) return 0;
   FusedParams p{};
   p.C1 = static_cast<int>(C1); p.N1 = static_cast<int>(N1); p.N2 = static_cast<int>(N2); p.w_layout = w_layout;
+  if (dtype != EGS_F32) return configure_tensor_pair16(p) != 0 ? 1 : 0;
   return configure_tensor_fused_pair(p, precision) != 0 ? 1 : 0;
 }
 
 int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, const void* Ind, void* Mid, void* Dst,
                             int64_t B, int64_t T, int64_t E, int64_t K, int64_t C1, int64_t N1, int64_t N2, int w_layout,
-                            int zero_output, int dtype, int index_dtype, int precision, int32_t* status_word,
-                            void* cuda_stream) {
+                            int zero_output, int dtype, int index_dtype, int precision, void* workspace,
+                            size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
   egs_dims d1{B, T, E, K, C1, N1}, d2{B, T, E, K, N1, N2};
   if (int rc = check_dims(&d1)) return rc;
   if (int rc = check_dims(&d2)) return rc;
@@ -214,26 +238,68 @@ int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, con
     return EGS_ERR_INVALID_ARGUMENT;
   if (!egs_fused_pair_eligible(C1, N1, N2, w_layout, dtype, precision)) return EGS_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  const size_t dst_bytes = static_cast<size_t>(B) * T * N2 * sizeof(float);
+  const size_t n_dst = static_cast<size_t>(B) * T * N2;
+  const size_t dst_bytes = n_dst * elem_size(dtype);
   if (dst_bytes > 0 && !Dst) return EGS_ERR_INVALID_ARGUMENT;
-  if (zero_output && dst_bytes > 0) {
-    cudaError_t err = launch_fill_zero(Dst, dst_bytes, st);
-    if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
-  }
-  if (B * E * K == 0) return EGS_OK;
-  if (!Src || !W1 || !W2 || !Ind || !Mid || !Dst) return EGS_ERR_INVALID_ARGUMENT;
-  if (!aligned16(Src) || !aligned16(W1) || !aligned16(W2) || !aligned16(Mid) || !aligned16(Dst)) return EGS_ERR_UNSUPPORTED;
+  const bool no_work = (B * E * K == 0);
+  if (!no_work && (!Src || !W1 || !W2 || !Ind || !Mid || !Dst)) return EGS_ERR_INVALID_ARGUMENT;
+  if (!no_work && (!aligned16(Src) || !aligned16(W1) || !aligned16(W2) || !aligned16(Mid) || !aligned16(Dst)))
+    return EGS_ERR_UNSUPPORTED;
   FusedParams p{};
-  p.Src = Src; p.W1 = W1; p.W2 = W2; p.Ind = Ind; p.Mid = Mid; p.Dst = static_cast<float*>(Dst); p.status = status_word;
+  p.Src = Src; p.W1 = W1; p.W2 = W2; p.Ind = Ind; p.Mid = Mid; p.status = status_word;
   p.B = static_cast<int>(B); p.T = static_cast<int>(T); p.E = static_cast<int>(E); p.K = static_cast<int>(K);
   p.C1 = static_cast<int>(C1); p.N1 = static_cast<int>(N1); p.N2 = static_cast<int>(N2);
   p.M = static_cast<int>(B * K);
   p.w_layout = w_layout; p.index_dtype = index_dtype;
-  const size_t smem = configure_tensor_fused_pair(p, precision);
+
+  if (dtype == EGS_F32) {
+    if (zero_output && dst_bytes > 0) {
+      cudaError_t err = launch_fill_zero(Dst, dst_bytes, st);
+      if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+    }
+    if (no_work) return EGS_OK;
+    p.Dst = static_cast<float*>(Dst);
+    const size_t smem = configure_tensor_fused_pair(p, precision);
+    if (smem == 0) return EGS_ERR_UNSUPPORTED;
+    cudaError_t err = launch_tensor_fused_pair(p, precision, smem, st);
+    if (err != cudaSuccess) return fail_cuda(err, "gather_scatter_pair launch");
+    return EGS_OK;
+  }
+
+  // 16-bit tensors: the scatter half works like egs_gemm_scatter (same scratch layout, same planning step)
+  if (dst_bytes == 0) return EGS_OK;
+  if (no_work) {
+    if (zero_output) {
+      cudaError_t err = launch_fill_zero(Dst, dst_bytes, st);
+      if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
+    }
+    return EGS_OK;
+  }
+  const size_t need = egs_scatter_workspace_bytes(B, T, N2, dtype);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  const size_t counter_bytes = (static_cast<size_t>(B) * T * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  int* plan = reinterpret_cast<int*>(ws);
+  int* counters = reinterpret_cast<int*>(ws + 256);
+  float* acc = reinterpret_cast<float*>(ws + 256 + counter_bytes);
+  cudaError_t err = launch_fill_zero(ws, 256 + counter_bytes, st);
+  if (err == cudaSuccess)
+    err = launch_scatter_plan(Ind, index_dtype, p.B, p.T, p.E, p.K, counters, plan, kDirect16Limit, status_word, st);
+  if (err == cudaSuccess) err = launch_scatter_init(plan, acc, Dst, n_dst, zero_output, dtype, st);
+  if (err != cudaSuccess) return fail_cuda(err, "scatter scratch init");
+  p.Dst = acc; p.Out16 = Dst; p.plan = plan;
+  const double act_bytes = static_cast<double>(B) * T * N2 * 4.0;
+  const double w_bytes = static_cast<double>(E) * N1 * (static_cast<double>(C1) + N2) * elem_size(dtype);
+  // Row-block order: experts fastest keeps the token rows being gathered from and added to (a few batch elements at a time)
+  // resident in L2 while every expert's two weight tiles stream through it; worth it when the token rows exceed L2
+  // and all weights fit in it next to them.
+  p.expert_fastest = (act_bytes > 96e6 && w_bytes < 100e6) ? 1 : 0;
+  const size_t smem = configure_tensor_pair16(p);
   if (smem == 0) return EGS_ERR_UNSUPPORTED;
-  cudaError_t err = launch_tensor_fused_pair(p, precision, smem, st);
+  err = launch_tensor_pair16(p, dtype, smem, st);
   if (err != cudaSuccess) return fail_cuda(err, "gather_scatter_pair launch");
-  return EGS_OK;
+  err = launch_scatter_finish(plan, acc, Dst, n_dst, dtype, st);
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "scatter scratch convert");
 }
 
 size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype) {
@@ -330,7 +396,7 @@ static int dweight_impl(const void* Xsrc, const void* Ysrc, const void* Ind, voi
 // ------------------------------------------------------------------------------------------------
 #define EGS_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)          /* 16 MiB, held by every device that loads the library */
 static __device__ __align__(256) float g_static_dw_scratch[EGS_STATIC_SCRATCH_FLOATS];
-static float* g_static_dw_scratch_addr[64] = {};             /* per device ordinal, filled on first use */
+static std::atomic<float*> g_static_dw_scratch_addr[64];     /* per device ordinal, filled on first use */
 
 int egs_dweight(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T, int64_t E,
                 int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype, int precision, int path,
@@ -349,28 +415,33 @@ int egs_dweight_prezeroed(const void* Xsrc, const void* Ysrc, const void* Ind, v
 int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* Ind, void* out, int64_t B, int64_t T,
                                int64_t E, int64_t K, int64_t FG, int64_t FD, int out_layout, int dtype, int index_dtype,
                                int precision, int path, int32_t* status_word, void* cuda_stream) {
-  // size check first: it needs no device
+  // size check first: it needs no device.  float32 tensors accumulate straight into `out` and never touch the
+  // scratch, so the limit applies to 16-bit tensors only.
   if (E < 0 || FG < 0 || FD < 0) return EGS_ERR_INVALID_ARGUMENT;
-  if (static_cast<double>(E) * static_cast<double>(FG) * static_cast<double>(FD) > static_cast<double>(EGS_STATIC_SCRATCH_FLOATS)) {
+  const double elements = static_cast<double>(E) * static_cast<double>(FG) * static_cast<double>(FD);
+  if (dtype != EGS_F32 && elements > static_cast<double>(EGS_STATIC_SCRATCH_FLOATS)) {
     std::snprintf(g_cuda_error, sizeof(g_cuda_error),
-                  "egs_dweight_static_scratch: E*FG*FD = %lld elements exceed the built-in scratch of %d",
-                  static_cast<long long>(E * FG * FD), EGS_STATIC_SCRATCH_FLOATS);
+                  "egs_dweight_static_scratch: E*FG*FD = %.0f elements exceed the built-in scratch of %d", elements,
+                  EGS_STATIC_SCRATCH_FLOATS);
     return EGS_ERR_TOO_LARGE;
   }
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return fail_cuda(err, "cudaGetDevice");
   if (dev < 0 || dev >= 64) return EGS_ERR_TOO_LARGE;
-  if (g_static_dw_scratch_addr[dev] == nullptr) {            // set-up: first call on this device
-    float* addr = nullptr;
-    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_dw_scratch);
-    if (err != cudaSuccess || addr == nullptr) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
-    g_static_dw_scratch_addr[dev] = addr;
+  float* scratch = g_static_dw_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {                                  // set-up: first call on this device
+    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_static_dw_scratch);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
+    if (scratch == nullptr) {
+      std::snprintf(g_cuda_error, sizeof(g_cuda_error), "cudaGetSymbolAddress(static scratch) returned a null address");
+      return EGS_ERR_CUDA;
+    }
+    g_static_dw_scratch_addr[dev].store(scratch, std::memory_order_release);   // every thread stores the same value
   }
   // egs_dweight clears the part of the scratch it accumulates into before use and reads back only what it wrote
-  return egs_dweight(Xsrc, Ysrc, Ind, out, B, T, E, K, FG, FD, out_layout, dtype, index_dtype, precision, path,
-                     g_static_dw_scratch_addr[dev], sizeof(float) * static_cast<size_t>(EGS_STATIC_SCRATCH_FLOATS),
-                     status_word, cuda_stream);
+  return egs_dweight(Xsrc, Ysrc, Ind, out, B, T, E, K, FG, FD, out_layout, dtype, index_dtype, precision, path, scratch,
+                     sizeof(float) * static_cast<size_t>(EGS_STATIC_SCRATCH_FLOATS), status_word, cuda_stream);
 }
 
 size_t egs_static_scratch_max_elements(void) { return EGS_STATIC_SCRATCH_FLOATS; }

@@ -78,15 +78,17 @@ struct DWeightParams {
   int row_tiles;      // tensor path: 128-feature accumulator tiles per CTA over FG (1 or 2)
 };
 
-// Fused pair G -> S on float32 tensors (tensor path only):  Mid = gather(Src) x W1[e] is stored as slot rows AND fed,
-// from shared memory, into  Dst[token rows] += Mid x W2[e].
+// Fused pair G -> S (tensor path only):  Mid = gather(Src) x W1[e] is stored as slot rows AND fed, without leaving the
+// SM (shared memory for float32 tensors, tensor memory for 16-bit ones), into  Dst[token rows] += Mid x W2[e].
 struct FusedParams {
   const void* Src;     // token rows [B*T, C1]
   const void* W1;      // [E, C1, N1] (EGS_W_CN) or [E, N1, C1] (EGS_W_NC)
   const void* W2;      // [E, N1, N2] (EGS_W_CN) or [E, N2, N1] (EGS_W_NC)
   const void* Ind;     // [B, E, K]
   void* Mid;           // slot rows [B*E*K, N1], overwritten
-  float* Dst;          // token rows [B*T, N2], added to
+  float* Dst;          // float32 token rows [B*T, N2], added to (16-bit tensors: the accumulation rows of the scratch)
+  void* Out16;         // 16-bit tensors: the output token rows [B*T, N2] that direct 16-bit additions go to
+  const int* plan;     // 16-bit tensors: device flag, see RowGemmParams::plan
   int32_t* status;
   int B, T, E, K, C1, N1, N2;
   int M;               // B*K
@@ -94,6 +96,8 @@ struct FusedParams {
   int index_dtype;
   int BN1, BN2;        // MMA widths (multiples of 16)
   int stages;
+  int expert_fastest;  // 16-bit kernel: order of the row blocks a CTA walks (1: experts vary fastest)
+  uint32_t slot_bytes; // 16-bit kernel: bytes of one ring slot
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -123,6 +127,17 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
 // Fused pair: `configure` returns 0 when the shape does not fit the kernel (the caller then runs G and S).
 size_t configure_tensor_fused_pair(FusedParams& p, int precision);
 cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t smem_bytes, cudaStream_t st);
+// Fused pair for 16-bit tensors (persistent kernel, egs_pair16.cu); same conventions.
+size_t configure_tensor_pair16(FusedParams& p);
+cudaError_t launch_tensor_pair16(const FusedParams& p, int dtype, size_t smem_bytes, cudaStream_t st);
+
+// Opaque 128-byte TMA tensor map (CUtensorMap of the driver API) and its encoder for a dense 3-D tensor of 16-bit
+// elements, dims[0] innermost, 128-byte swizzle, out-of-range elements read as zero.  Returns false when the driver
+// refuses the geometry (strides must be multiples of 16 bytes, box sides at most 256).
+struct alignas(64) TensorMap3 {
+  unsigned char bytes[128];
+};
+bool encode_tensor_map_16bit(TensorMap3* out, const void* base, const unsigned long long dims[3], const unsigned box[3]);
 
 // Bounded-wait self-test (see the kernel): out = two ints on the device.
 cudaError_t launch_wait_timeout_selftest(int32_t* status, int* out, long long limit_cycles, cudaStream_t st);

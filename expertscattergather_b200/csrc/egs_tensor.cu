@@ -32,393 +32,11 @@
 // hi = top 19 bits and lo = tf32(x - hi) and issues lo*hi + hi*lo + hi*hi into the same accumulator, which
 // restores ~fp32 product accuracy (the reference computes fp32 dots with allow_tf32=False,
 // egs/triton_kernels.py:389).  16-bit tensors: kind::f16 with fp32 accumulation.
-#include <cstdlib>
-
-#include "egs_internal.cuh"
+#include "egs_tcgen05.cuh"
 
 namespace egs {
 
 namespace {
-
-constexpr int kProducerWarps = 8;
-constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = kProducerThreads + 32;
-constexpr int kTileM = 128;
-constexpr int kMaxStages = 8;
-constexpr uint32_t kHeaderBytes = 3072;       // row kernel: barriers + two row tables
-constexpr uint32_t kHeaderBytesD = 1024;      // weight-gradient kernel: barriers only (the row tables are unused)
-constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 clocks
-
-constexpr int kMaxRowsPerSplit = 4096;   // operator D: contraction rows one CTA may own (row table in smem)
-
-struct __align__(16) SmemHeader {
-  unsigned long long full[kMaxStages];
-  unsigned long long empty[kMaxStages];
-  unsigned long long done;
-  uint32_t tmem_base;
-  uint32_t abort_flag;
-  int row_a[2 * kTileM];   // rowgemm: source row index per CTA row (-1 = masked)
-  int row_o[2 * kTileM];   // rowgemm: destination row index per CTA row (-1 = masked)
-};
-static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header does not fit");
-
-// ------------------------------------------------------------------------------------------------
-// PTX wrappers
-// ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-// Hardware arrive on an mbarrier once all cp.async copies this thread has issued so far have landed.
-__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_pending(int n) {
-  switch (n) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-  }
-}
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this or another thread ran out of time).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          int32_t* status, long long limit_cycles = kWaitLimitCycles) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  for (;;) {
-    if (mbar_try(bar, parity)) return true;
-    if (((++spins) & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > limit_cycles) {
-        *abort_flag = 1u;
-        if (status) atomicOr(status, EGS_STATUS_PIPELINE_TIMEOUT);
-        return false;
-      }
-    }
-  }
-}
-
-// One lane polls, the warp shares the outcome (keeps 31 lanes per warp off the barrier word).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                               int32_t* status, int lane) {
-  uint32_t ok = 1u;
-  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-template <bool TF32>
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  if (TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-// 16 consecutive fp32 accumulator columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-// 32 consecutive fp32 accumulator columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, sm_100 version field set.  layout_type 2 = 128-byte swizzle (16-byte
-// granules, 8-row atoms); 1 = 128-byte swizzle with 32-byte granules and 4-row atoms, the only layout the
-// tensor core accepts for MN-major (transposed) 32-bit operands.
-constexpr uint32_t kSwizzle128 = 2, kSwizzle128Base32 = 1;
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                                   uint32_t layout_type = kSwizzle128) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;   // descriptor version of this architecture
-  d |= static_cast<uint64_t>(layout_type) << 61;
-  return d;
-}
-// Instruction descriptor: fp32 accumulator, A and B of one format (0 f16, 1 bf16, 2 tf32).
-__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t a_mn_major, uint32_t b_mn_major, uint32_t m,
-                                               uint32_t n) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
-         ((m >> 4) << 24);
-}
-
-// Address of (row r, 16-byte chunk c) inside a tile in the format described at the top of the file.
-// BASE32 selects the 32-byte-granule swizzle: rows stay 128 bytes apart, but the XOR acts on the 32-byte
-// pair index with the row index modulo 4 (atoms of 4 rows, 512 bytes).
-template <bool BASE32>
-__device__ __forceinline__ uint32_t tile_addr(uint32_t base, uint32_t seg_stride, int r, int c) {
-  const uint32_t row = base + static_cast<uint32_t>(c >> 3) * seg_stride + static_cast<uint32_t>(r) * 128u;
-  if (BASE32) return row + (static_cast<uint32_t>(((c & 7) >> 1) ^ (r & 3)) << 5) + (static_cast<uint32_t>(c & 1) << 4);
-  return row + (static_cast<uint32_t>((c & 7) ^ (r & 7)) << 4);
-}
-
-// In-place hi/lo split of one 16-byte chunk of float32 values (strict mode).
-__device__ __forceinline__ void split_chunk(uint32_t addr, uint32_t lo_offset) {
-  uint32_t v[4], lo[4];
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t hi = v[i] & 0xFFFFE000u;
-    const float rem = __uint_as_float(v[i]) - __uint_as_float(hi);
-    lo[i] = (__float_as_uint(rem) + 0x1000u) & 0xFFFFE000u;   // round to tf32 (nearest, ties away) with integer ops
-    v[i] = hi;
-  }
-  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
-  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr + lo_offset), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3])
-               : "memory");
-}
-
-template <typename T> struct Elem;
-template <> struct Elem<float> { static constexpr uint32_t fmt = 2; static constexpr bool tf32 = true; };
-template <> struct Elem<__half> { static constexpr uint32_t fmt = 0; static constexpr bool tf32 = false; };
-template <> struct Elem<__nv_bfloat16> { static constexpr uint32_t fmt = 1; static constexpr bool tf32 = false; };
-
-// Optional phase trace (compile with -DEGS_TRACE): CTA (0,0,0) records globaltimer stamps of its phases.
-#ifdef EGS_TRACE
-__device__ unsigned long long g_trace[256];
-__device__ __forceinline__ void trace_mark(int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[slot] = t;
-  }
-}
-#define EGS_MARK(slot) trace_mark(slot)
-// cycle accounting of one role of CTA 0:  EGS_TIC(); ...wait...; EGS_TOC(slot) adds the elapsed clock64 ticks
-#define EGS_TIC() const long long egs_tic_ = clock64()
-#define EGS_TOC(slot)                                                          \
-  do {                                                                         \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_trace[slot] += static_cast<unsigned long long>(clock64() - egs_tic_); \
-  } while (0)
-#else
-#define EGS_MARK(slot)
-#define EGS_TIC()
-#define EGS_TOC(slot)
-#endif
-
-// ---- epilogue helpers ----
-__device__ __forceinline__ uint32_t pack2(__half*, uint32_t a, uint32_t b) {
-  const __half2 h = __floats2half2_rn(__uint_as_float(a), __uint_as_float(b));
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ uint32_t pack2(__nv_bfloat16*, uint32_t a, uint32_t b) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-// Warp-level transpose of a 32-row x 32-column fp32 accumulator block through a 4 KB shared-memory tile.
-// In tensor memory one thread owns one row, which would make every global access of a warp touch 32
-// different rows (16 bytes each).  After the transpose 8 lanes cover 128 contiguous bytes of one row, 4 rows
-// per instruction; for red.global.add that pattern measured ~3x the throughput of the row-per-thread one.
-//   emit(row_in_block, first_column, x0, x1, x2, x3) is called 8 times per lane.
-template <class Emit>
-__device__ __forceinline__ void warp_block_emit(uint32_t taddr, uint32_t tile, int lane, bool have_acc, Emit&& emit) {
-  uint32_t v[32];
-#ifdef EGS_TRACE
-  const bool tr = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && ((threadIdx.x >> 5) & 7) == 0);
-  const long long c0 = clock64();
-#endif
-  if (have_acc) {
-    tmem_ld32(taddr, v);
-    tmem_ld_wait();
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = 0u;
-  }
-#ifdef EGS_TRACE
-  const long long c1 = clock64();
-#endif
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + lane * 128u + (static_cast<uint32_t>(j ^ (lane & 7)) << 4)),
-                 "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
-                 : "memory");
-  __syncwarp();
-  const int j = lane & 7;
-  uint32_t x[8][4];
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {      // all reads first, so that their latencies overlap
-    const int row = it * 4 + (lane >> 3);
-    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(x[it][0]), "=r"(x[it][1]), "=r"(x[it][2]), "=r"(x[it][3])
-                 : "r"(tile + row * 128u + (static_cast<uint32_t>(j ^ (row & 7)) << 4))
-                 : "memory");
-  }
-  __syncwarp();                         // the tile may be overwritten from here on
-#ifdef EGS_TRACE
-  const long long c2 = clock64();
-#endif
-#pragma unroll
-  for (int it = 0; it < 8; ++it) emit(it * 4 + (lane >> 3), j * 4, x[it][0], x[it][1], x[it][2], x[it][3]);
-#ifdef EGS_TRACE
-  if (tr) {
-    const long long c3 = clock64();
-    g_trace[232] += static_cast<unsigned long long>(c1 - c0);   // tcgen05.ld + wait
-    g_trace[233] += static_cast<unsigned long long>(c2 - c1);   // transpose through shared memory
-    g_trace[234] += static_cast<unsigned long long>(c3 - c2);   // emit (stores / reds)
-    g_trace[235] += 1ull;
-  }
-#endif
-}
-// Same transpose for a 32-row x 64-column block (8 KB tile): every lane ends up with 8 consecutive columns of
-// one row, so 8 lanes cover 64 columns - 128 contiguous bytes of a 16-bit row per instruction.
-//   emit(row_in_block, first_column, x[8]) is called 8 times per lane.
-template <class Emit>
-__device__ __forceinline__ void warp_block_emit64(uint32_t taddr, uint32_t tile, int lane, Emit&& emit) {
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    uint32_t v[32];
-    tmem_ld32(taddr + h * 32, v);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + lane * 256u + (static_cast<uint32_t>((h * 8 + j) ^ (lane & 7)) << 4)),
-                   "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
-                   : "memory");
-  }
-  __syncwarp();
-  const int j = lane & 7;
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int row = it * 4 + (lane >> 3);
-    uint32_t x[8];
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(x[4 * q]), "=r"(x[4 * q + 1]), "=r"(x[4 * q + 2]), "=r"(x[4 * q + 3])
-                   : "r"(tile + row * 256u + (static_cast<uint32_t>((2 * j + q) ^ (row & 7)) << 4))
-                   : "memory");
-    emit(row, j * 8, x);
-  }
-  __syncwarp();
-}
-__device__ __forceinline__ void red8(__nv_bfloat16* dst, const uint32_t (&x)[8]) {
-  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(pack2(dst, x[0], x[1])),
-               "r"(pack2(dst, x[2], x[3])), "r"(pack2(dst, x[4], x[5])), "r"(pack2(dst, x[6], x[7]))
-               : "memory");
-}
-__device__ __forceinline__ void red8(__half* dst, const uint32_t (&x)[8]) {
-  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(pack2(dst, x[0], x[1])),
-               "r"(pack2(dst, x[2], x[3])), "r"(pack2(dst, x[4], x[5])), "r"(pack2(dst, x[6], x[7]))
-               : "memory");
-}
-__device__ __forceinline__ void red8(float*, const uint32_t (&)[8]) {}   // never taken: direct adds are 16-bit only
-// Bulk asynchronous reduction: adds `bytes` (multiple of 16) of elements staged in shared memory to global memory.
-// The copy engine reads the shared memory after the instruction has issued: the staging buffer may be rewritten
-// only after bulk_wait_read, and the issuing thread's own writes need fence.proxy.async before the instruction.
-__device__ __forceinline__ void bulk_reduce_add(__nv_bfloat16* dst, uint32_t src_smem, uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_reduce_add(__half* dst, uint32_t src_smem, uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-constexpr uint32_t kBulkRowPitch = 144;                  // 128 staged bytes per row + 16: conflict-free 16-byte stores
-constexpr uint32_t kBulkBufBytes = 32 * kBulkRowPitch;   // one 32-row staging buffer
-__device__ __forceinline__ void red4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(__uint_as_float(x0)), "f"(__uint_as_float(x1)),
-               "f"(__uint_as_float(x2)), "f"(__uint_as_float(x3))
-               : "memory");
-}
-__device__ __forceinline__ void red4(__nv_bfloat16* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-  asm volatile("red.global.add.noftz.v2.bf16x2 [%0], {%1,%2};" ::"l"(dst), "r"(pack2(dst, x0, x1)), "r"(pack2(dst, x2, x3)) : "memory");
-}
-__device__ __forceinline__ void red4(__half* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-  asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1,%2};" ::"l"(dst), "r"(pack2(dst, x0, x1)), "r"(pack2(dst, x2, x3)) : "memory");
-}
-__device__ __forceinline__ void store4(float* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-  *reinterpret_cast<uint4*>(dst) = make_uint4(x0, x1, x2, x3);
-}
-template <typename T>
-__device__ __forceinline__ void store4(T* dst, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-  *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(dst, x0, x1), pack2(dst, x2, x3));
-}
-
-__device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
-  uint32_t c = 32;
-  while (c < static_cast<uint32_t>(bn)) c <<= 1;
-  return c;
-}
-
-// The dynamic shared memory is declared 1024-byte aligned (the swizzle atoms need it).  Should a launch ever
-// hand out a differently aligned base, the CTA refuses to work and reports EGS_STATUS_INTERNAL.
-__device__ __forceinline__ bool smem_misaligned(const void* raw) { return (smem_u32(raw) & 1023u) != 0u; }
-
-
 
 // ------------------------------------------------------------------------------------------------
 // Pipeline pieces shared by the two kernels
@@ -442,6 +60,7 @@ __device__ __forceinline__ uint32_t pipe_setup(const Pipe& pp, uint32_t full_cou
       mbar_init(smem_u32(&hdr->empty[s]), 1);
     }
     mbar_init(smem_u32(&hdr->done), 1);
+    mbar_init(smem_u32(&hdr->drain), 1);
     fence_mbar_init();
     // A launch that follows a timed-out one on the same status word does no work (keeps a broken pipeline
     // from costing one wait limit per wave of CTAs).
@@ -459,19 +78,13 @@ __device__ __forceinline__ uint32_t pipe_setup(const Pipe& pp, uint32_t full_cou
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (tid == 0) EGS_MARK(1);
   return hdr->tmem_base;
 }
 
-__device__ __forceinline__ void pipe_teardown(uint32_t tmem_base, uint32_t tmem_cols, int warp) {
-  if (threadIdx.x == 0) EGS_MARK(9);
+__device__ __forceinline__ void pipe_teardown(const Pipe& pp, uint32_t tmem_base, uint32_t tmem_cols, int warp) {
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) EGS_MARK(10);
-  if (warp == kProducerWarps) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
+  if (warp == kProducerWarps) tmem_release(tmem_base, tmem_cols, smem_u32(&pp.hdr->drain), pp.abort_flag, threadIdx.x & 31);
 }
 
 // Common end of every producer variant: drain own copies, then wait (warp-uniformly) for the accumulator.
@@ -481,7 +94,6 @@ __device__ __forceinline__ bool producer_finish(const Pipe& pp, int lane, bool a
   alive = __all_sync(0xffffffffu, alive);
   if (alive && pp.nk > 0) alive = mbar_wait_warp(smem_u32(&pp.hdr->done), 0u, pp.abort_flag, pp.status, lane);
   if (alive) tc_fence_after();
-  if (threadIdx.x == 0) EGS_MARK(8);
   return alive;
 }
 
@@ -495,16 +107,10 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
   if (!STRICT) {
     for (int kt = 0; kt < nk; ++kt) {
       const int slot = kt % stages, use = kt / stages;
-      {
-        EGS_TIC();
-        if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
-        if (threadIdx.x == 0) EGS_TOC(248);
-      }
+      if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, pp.abort_flag, pp.status, lane);
       if (!alive) break;
-      if (threadIdx.x == 0 && kt < 64) EGS_MARK(32 + kt);
       issue(kt, pp.tiles0 + slot * pp.stage_bytes);
       cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
-      if (threadIdx.x == 0 && kt < 64) EGS_MARK(96 + kt);
     }
   } else {
     const int dist = stages - 1;
@@ -512,21 +118,14 @@ __device__ __forceinline__ bool run_producer(const Pipe& pp, int lane, Issue&& i
       if (kt < nk) issue(kt, pp.tiles0 + (kt % stages) * pp.stage_bytes);
       cp_async_commit();
     }
-    if (threadIdx.x == 0) EGS_MARK(2);
     for (int kc = 0; kc < nk; ++kc) {
       cp_async_wait_pending(dist - 1);
-      if (threadIdx.x == 0 && kc == 0) EGS_MARK(3);
-      if (threadIdx.x == 0 && kc < 8) EGS_MARK(200 + kc);
       if (alive) {
         split(kc, pp.tiles0 + (kc % stages) * pp.stage_bytes);
-        if (threadIdx.x == 0 && kc < 8) EGS_MARK(208 + kc);
         fence_proxy_async_smem();
-        if (threadIdx.x == 0 && kc < 8) EGS_MARK(216 + kc);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->full[kc % stages]));
       }
-      if (threadIdx.x == 0 && kc == 0) EGS_MARK(4);
-      if (threadIdx.x == 0 && kc == nk - 1) EGS_MARK(5);
       const int kt = kc + dist;
       if (kt < nk && alive) {
         const int use = kt / stages;
@@ -564,32 +163,15 @@ template <class Mma>
 __device__ __forceinline__ void run_mma_lane(const Pipe& pp, Mma&& mma) {
   SmemHeader* hdr = pp.hdr;
   bool ok = true;
-#ifdef EGS_TRACE
-  const long long lane_t0 = clock64();
-#endif
   for (int ks = 0; ks < pp.nk; ++ks) {
     const int slot = ks % pp.stages;
-    {
-      EGS_TIC();
-      ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / pp.stages) & 1, pp.abort_flag, pp.status);
-      EGS_TOC(247);
-    }
+    ok = mbar_wait(smem_u32(&hdr->full[slot]), (ks / pp.stages) & 1, pp.abort_flag, pp.status);
     if (!ok) break;
     tc_fence_after();
-    if (ks == 0) EGS_MARK(6);
-    if (ks < 64) EGS_MARK(160 + ks);
     mma(ks, pp.tiles0 + slot * pp.stage_bytes);
-    if (ks < 8) EGS_MARK(224 + ks);
     umma_commit(smem_u32(&hdr->empty[slot]));
   }
   if (ok && pp.nk > 0) umma_commit(smem_u32(&hdr->done));
-#ifdef EGS_TRACE
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-    g_trace[249] += static_cast<unsigned long long>(clock64() - lane_t0);
-    g_trace[250] += static_cast<unsigned long long>(pp.nk);
-  }
-#endif
-  EGS_MARK(7);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -618,7 +200,6 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) EGS_MARK(0);
   const int e = p.expert_fastest ? blockIdx.x : blockIdx.z;
   const int m0 = (p.expert_fastest ? blockIdx.z : blockIdx.x) * kRows;
   const int n0 = blockIdx.y * p.BN;
@@ -946,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
     }
     __syncwarp();
   }
-  pipe_teardown(tmem_base, tmem_cols, warp);
+  pipe_teardown(pp, tmem_base, tmem_cols, warp);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -979,6 +560,7 @@ struct __align__(16) PersistHeader {
   unsigned long long empty[kMaxStages];
   unsigned long long acc_full[2];
   unsigned long long acc_empty[2];
+  unsigned long long drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -1039,7 +621,6 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
   const uint32_t tiles0 = xpose0 + ((kPersistMaxEpilogueWarps * xpose_tile + 1023u) & ~1023u);   // stage ring
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) EGS_MARK(0);
   const bool w_nc = (p.w_layout == EGS_W_NC);
   const int m_tiles = (p.M + kTileM - 1) / kTileM;
   const int n_tiles = (p.N + p.BN - 1) / p.BN;
@@ -1065,6 +646,7 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
       mbar_init(smem_u32(&hdr->acc_full[b]), 1);
       mbar_init(smem_u32(&hdr->acc_empty[b]), kPersistEpilogueWarps);
     }
+    mbar_init(smem_u32(&hdr->drain), 1);
     fence_mbar_init();
     hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
     if (smem_misaligned(smem_raw)) {
@@ -1133,13 +715,8 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
         const bool tile_full = a_full && (nc_full || cn_full);
         for (int kt = 0; kt < nk; ++kt, ++g) {
           const int slot = g % stages, use = g / stages;
-          {
-            EGS_TIC();
-            if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
-            if (tid == 0) EGS_TOC(244);
-          }
+          if (use > 0) alive = mbar_wait_warp(smem_u32(&hdr->empty[slot]), (use - 1) & 1, abort_flag, p.status, lane);
           if (!alive) break;
-          if (tid == 0 && g < 48) EGS_MARK(32 + g);
           const uint32_t base = tiles0 + slot * stage_bytes;
           const int k0 = kt * KE;
           const long long koff = static_cast<long long>(k0) * ES;
@@ -1184,7 +761,6 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
             }
           }
           cp_async_mbar_arrive_noinc(smem_u32(&hdr->full[slot]));
-          if (tid == 0 && g < 48) EGS_MARK(80 + g);
         }
       }
     }
@@ -1214,15 +790,9 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
         const int n0 = nt * p.BN;
         const int bn = min(p.BN, ((p.N - n0) + 15) & ~15);
         const int buf = t & 1;
-        {
-          EGS_TIC();
-          alive = mbar_wait_warp(smem_u32(&hdr->acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, lane);
-          if (ew == 0 && lane == 0) EGS_TOC(242);
-        }
+        alive = mbar_wait_warp(smem_u32(&hdr->acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, lane);
         if (!alive) break;
         tc_fence_after();
-        if (ew == 0 && lane == 0 && t < 12) EGS_MARK(176 + 2 * t);
-        EGS_TIC();
         const int nblk = (bn + 31) >> 5;
         if (bulk) {
           const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + buf * acc_cols;
@@ -1272,8 +842,6 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
                           });
         }
         // hand the accumulator buffer back to the MMA lane
-        if (ew == 0 && lane == 0 && t < 12) EGS_MARK(177 + 2 * t);
-        if (ew == 0 && lane == 0) EGS_TOC(243);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->acc_empty[buf]));
@@ -1289,9 +857,6 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
       const uint64_t a_adv = 32u >> 4, b_adv = (w_nc ? 32u : UK * 128u) >> 4;
       bool ok = true;
       int g = 0, t = 0;
-#ifdef EGS_TRACE
-      const long long lane_t0 = clock64();
-#endif
       for (int rb = blockIdx.x; rb < row_blocks && ok; rb += gridDim.x) {
         for (int nt = 0; nt < n_tiles && ok; ++nt, ++t) {
           const int n0 = nt * p.BN;
@@ -1299,21 +864,16 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
           const uint32_t idesc = make_idesc(Elem<T>::fmt, 0u, w_nc ? 0u : 1u, kTileM, static_cast<uint32_t>(bn));
           const int buf = t & 1;
           if (t >= 2) {
-            EGS_TIC();
             ok = mbar_wait(smem_u32(&hdr->acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status);
-            EGS_TOC(241);
             if (!ok) break;
             tc_fence_after();
           }
           const uint32_t d = tmem_base + buf * acc_cols;
           for (int ks = 0; ks < nk; ++ks, ++g) {
             const int slot = g % stages;
-            EGS_TIC();
             ok = mbar_wait(smem_u32(&hdr->full[slot]), (g / stages) & 1, abort_flag, p.status);
-            EGS_TOC(240);
             if (!ok) break;
             tc_fence_after();
-            if (g < 48) EGS_MARK(128 + g);
             const uint32_t a_hi = tiles0 + slot * stage_bytes;
             uint64_t ad = make_smem_desc(a_hi, 16u, 1024u);
             uint64_t bd = make_smem_desc(a_hi + b_off, b_lbo, b_sbo, b_lay);
@@ -1329,12 +889,6 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
           if (ok) umma_commit(smem_u32(&hdr->acc_full[buf]));
         }
       }
-#ifdef EGS_TRACE
-      if (blockIdx.x == 0) {
-        g_trace[245] += static_cast<unsigned long long>(clock64() - lane_t0);
-        g_trace[246] += static_cast<unsigned long long>(t);
-      }
-#endif
     }
     __syncwarp();
   }
@@ -1342,10 +896,7 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
   // ---- common exit ----
   tc_fence_before();
   __syncthreads();
-  if (warp == mma_warp) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
+  if (warp == mma_warp) tmem_release(tmem_base, tmem_cols, smem_u32(&hdr->drain), abort_flag, lane);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1375,7 +926,6 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_dweight_kern
   const uint32_t table_bytes = (static_cast<uint32_t>(p.rows_per_split) * 4u + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) EGS_MARK(0);
   const int e = blockIdx.z / p.splits;
   const int split = blockIdx.z - e * p.splits;
   const int f0 = blockIdx.x * (kTileM * MT);
@@ -1651,7 +1201,7 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_dweight_kern
     }
     __syncwarp();
   }
-  pipe_teardown(tmem_base, tmem_cols, warp);
+  pipe_teardown(pp, tmem_base, tmem_cols, warp);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1674,7 +1224,7 @@ constexpr uint32_t kFusedHeaderBytes = 3072;
 struct __align__(16) FusedHeader {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long acc1_done, mid_ready, acc2_done;
+  unsigned long long acc1_done, mid_ready, acc2_done, drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
   int row_tok[kTileM];    // token row of every tile row (-1 = masked): gather source and scatter target
@@ -1734,6 +1284,7 @@ __global__ void __launch_bounds__(17 * 32, 1) tensor_fused_pair_kernel(FusedPara
     mbar_init(smem_u32(&hdr->acc1_done), 1);
     mbar_init(smem_u32(&hdr->mid_ready), kEpiWarps);
     mbar_init(smem_u32(&hdr->acc2_done), 1);
+    mbar_init(smem_u32(&hdr->drain), 1);
     fence_mbar_init();
     hdr->abort_flag = (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & EGS_STATUS_PIPELINE_TIMEOUT)) ? 1u : 0u;
     if (smem_misaligned(smem_raw)) {
@@ -1974,10 +1525,7 @@ __global__ void __launch_bounds__(17 * 32, 1) tensor_fused_pair_kernel(FusedPara
   // ---- common exit ----
   tc_fence_before();
   __syncthreads();
-  if (warp == mma_warp) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
-  }
+  if (warp == mma_warp) tmem_release(tmem_base, tmem_cols, smem_u32(&hdr->drain), abort_flag, lane);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -2009,31 +1557,17 @@ constexpr size_t kSmemReservedPerCta = 1024;
 constexpr size_t kSmemMaxPerCta = 227 * 1024;
 constexpr int kSmCount = 148;
 
-// Tuning aids (read once): EGS_B200_TILE_N caps the tile width over N (multiple of 16, 16..256);
-// EGS_B200_STAGES caps the pipeline depth (>= 2).
-int env_int(const char* name) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : 0;
-}
-int tile_n_cap(int dflt) {
-  static const int env = env_int("EGS_B200_TILE_N");
-  if (env >= 16 && env <= 256) return (env / 16) * 16 < dflt ? (env / 16) * 16 : dflt;
-  return dflt;
-}
 
 // Pipeline depth: large grids aim at two CTAs per SM (the prologue and epilogue of one CTA overlap the main
 // loop of the other); grids that fit in one wave take the whole SM.
 int pick_stages(size_t fixed_bytes, size_t stage_bytes, long long ctas, bool allow_two_per_sm) {
-  static const int env = env_int("EGS_B200_STAGES");
-  static const int one_cta = env_int("EGS_B200_ONE_CTA");
   const size_t two = kSmemPerSm / 2 - kSmemReservedPerCta;
   int s = 0;
-  if (allow_two_per_sm && !one_cta && ctas > kSmCount && fixed_bytes + 2 * stage_bytes <= two)
+  if (allow_two_per_sm && ctas > kSmCount && fixed_bytes + 2 * stage_bytes <= two)
     s = static_cast<int>((two - fixed_bytes) / stage_bytes);
   else
     s = static_cast<int>((kSmemMaxPerCta - fixed_bytes) / stage_bytes);
   if (s > kMaxStages) s = kMaxStages;
-  if (env >= 2 && env < s) s = env;
   return s;
 }
 
@@ -2044,7 +1578,7 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int ke = 128 / es;
   int bn = (p.N + 15) & ~15;
-  const int cap = tile_n_cap(strict ? 128 : 256);
+  const int cap = strict ? 128 : 256;
   if (bn > cap) bn = cap;
   // strict float32 doubles every tile (hi + lo): when the grid is larger than one wave, 64-wide tiles keep a
   // 2-stage ring under half an SM's shared memory so that two CTAs share an SM
@@ -2058,23 +1592,20 @@ size_t configure_tensor_rowgemm(RowGemmParams& p, bool scatter, int dtype, int p
   const long long n_tiles = (p.N + bn - 1) / bn;
   // 256-row CTAs (two accumulators): when the grid still fills the SMs at least once, the contraction is long
   // enough for the deeper ring to matter, and the two accumulators fit in tensor memory
-  static const int mt_env = env_int("EGS_B200_ROW_TILES");
   const long long ctas2 = static_cast<long long>((p.M + 2 * kTileM - 1) / (2 * kTileM)) * n_tiles * p.E;
   // (the scatter epilogue dominates short contractions and profits from two CTAs per SM instead)
   const bool want2 = !strict && p.M >= 2 * kTileM && ctas2 >= kSmCount && p.C * es >= (scatter ? 4096 : 1024);
-  p.row_tiles = (mt_env == 1) ? 1 : (mt_env == 2 && !strict && p.M > kTileM) ? 2 : (want2 ? 2 : 1);
+  p.row_tiles = want2 ? 2 : 1;
   const size_t a_bytes = static_cast<size_t>(kTileM) * p.row_tiles * 128;
   const size_t stage_bytes = (a_bytes + b_bytes) * (strict ? 2 : 1);
   const long long ctas = static_cast<long long>((p.M + kTileM * p.row_tiles - 1) / (kTileM * p.row_tiles)) * n_tiles * p.E;
   // persistent variant (see its kernel): scatter problems with many tiles, non-strict arithmetic
-  static const int persist_env = getenv("EGS_B200_PERSISTENT") ? env_int("EGS_B200_PERSISTENT") : -1;
   const long long tiles1 = static_cast<long long>((p.M + kTileM - 1) / kTileM) * n_tiles * p.E;
   p.persistent = 0;
-  // direct 16-bit scatter adds go out as bulk reductions (tuning aid: EGS_B200_BULK_EPILOGUE=0 keeps the reds)
-  static const int bulk_env = getenv("EGS_B200_BULK_EPILOGUE") ? env_int("EGS_B200_BULK_EPILOGUE") : 1;
-  p.bulk_epilogue = (bulk_env && scatter && es == 2) ? 1 : 0;
+  // direct 16-bit scatter adds go out as bulk reductions
+  p.bulk_epilogue = (scatter && es == 2) ? 1 : 0;
   // (measured: it wins for contractions of up to four stages - the scatter of cfg4 and cfg2 - and loses for longer ones)
-  if (!strict && persist_env != 0 && ((scatter && p.C * es <= 512) || persist_env == 2) && tiles1 >= 2 * kSmCount) {
+  if (!strict && scatter && p.C * es <= 512 && tiles1 >= 2 * kSmCount) {
     const size_t st1 = static_cast<size_t>(kTileM) * 128 + b_bytes;
     size_t fixed_p = kPersistHeaderBytes + kPersistMaxEpilogueWarps * 4096;
     // 16-bit scatter: staging buffers for the bulk adds when the ring keeps three stages
@@ -2100,16 +1631,15 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   const bool strict = (dtype == EGS_F32 && precision == EGS_PREC_STRICT);
   const int kr = 128 / es;
   int bn = (p.FD + 15) & ~15;
-  const int cap = tile_n_cap(strict ? 64 : 256);   // strict: 64-wide tiles so that two CTAs share an SM
+  const int cap = strict ? 64 : 256;   // strict: 64-wide tiles so that two CTAs share an SM
   if (bn > cap) bn = cap;
   p.BN = bn;
   const size_t seg_stride = static_cast<size_t>(kr) * 128;
   const size_t nseg_b = (static_cast<size_t>(bn) * es + 127) / 128;
   // 256-feature CTAs (two accumulators): long contractions whose grid still covers the SMs, non-strict only
-  static const int mt_env = env_int("EGS_B200_DW_ROW_TILES");
   const long long tiles2 = static_cast<long long>((p.FG + 2 * kTileM - 1) / (2 * kTileM)) * ((p.FD + bn - 1) / bn) * p.E;
   const bool want2 = !strict && p.FG > kTileM && tiles2 >= kSmCount && p.M >= 16 * kr && bn * 2 <= 512;
-  p.row_tiles = (mt_env == 1) ? 1 : (mt_env == 2 && !strict && p.FG > kTileM) ? 2 : (want2 ? 2 : 1);
+  p.row_tiles = want2 ? 2 : 1;
   const size_t a_bytes = es * seg_stride * p.row_tiles;
   const size_t stage_bytes = (a_bytes + nseg_b * seg_stride) * (strict ? 2 : 1);
   // split the contraction so that the grid fills one wave of CTAs and no CTA owns more rows than the
@@ -2158,8 +1688,6 @@ size_t configure_tensor_fused_pair(FusedParams& p, int precision) {
   const size_t ntot = static_cast<size_t>((p.C1 + 31) / 32 + p.N1 / 32);
   if (ns > ntot) ns = ntot;
   if (ns > static_cast<size_t>(kMaxStages)) ns = kMaxStages;
-  static const int env = env_int("EGS_B200_STAGES");
-  if (env >= 2 && static_cast<size_t>(env) < ns) ns = env;
   if (ns < 2 || ns * stage_bytes < 8u * 4096u) return 0;                   // the ring doubles as the transpose tiles
   p.stages = static_cast<int>(ns);
   return fixed + ns * stage_bytes;
@@ -2292,9 +1820,3 @@ cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t
 
 }  // namespace egs
 
-#ifdef EGS_TRACE
-extern "C" int egs_debug_trace(unsigned long long* host_out, int n) {
-  if (n > 256) n = 256;
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, egs::g_trace, n * sizeof(unsigned long long)));
-}
-#endif

@@ -54,7 +54,10 @@ def _weight_grad_on_side_stream(Xsrc, Ysrc, Ind, out_layout):
 
 
 def _join_side(t):
+    """Joins the helper stream and queues the copy of the status word to its host mirror: once per backward call, after
+    its kernels, so that the next operator call raises if one of them reported invalid results."""
     torch.cuda.current_stream(t.device).wait_stream(ops.side_stream(t.device))
+    ops.publish_status(t.device)
 
 
 def _gather_backward(X, W, Ind, grad_output, out_dtype):

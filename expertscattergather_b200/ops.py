@@ -14,7 +14,7 @@ import torch
 from . import _lib
 
 __all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "fused_pair_preferred", "dweight", "fill_zero", "side_stream", "fill_stream", "set_precision", "get_precision", "set_path", "get_path",
-           "check_status", "reset_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
+           "check_status", "reset_status", "publish_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
 _PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR}
@@ -26,6 +26,7 @@ _state = {
     "debug": os.environ.get("EGS_B200_DEBUG", "0") not in ("0", "", "false"),
 }
 _status_words: dict[int, torch.Tensor] = {}
+_status_mirrors: dict[int, torch.Tensor] = {}     # pinned host copies of the status words (see publish_status)
 
 
 def set_precision(mode: str) -> None:
@@ -88,6 +89,49 @@ def reset_status(device=None) -> None:
     for idx, w in _status_words.items():
         if device is None or torch.device(device).index in (None, idx):
             w.zero_()
+            m = _status_mirrors.get(idx)
+            if m is not None:
+                m.zero_()
+
+
+def _status_text(idx: int, v: int) -> str:
+    msgs = []
+    if v & _lib.STATUS_INDEX_OUT_OF_RANGE:
+        msgs.append("an Ind value outside [0, T) was met (slot skipped)")
+    if v & _lib.STATUS_PIPELINE_TIMEOUT:
+        msgs.append("a bounded wait inside a tensor-core kernel ran out (results invalid)")
+    if v & _lib.STATUS_INTERNAL:
+        msgs.append("a tensor-core kernel found its shared memory misaligned and did no work (results invalid)")
+    return f"egs kernels on cuda:{idx} reported: " + "; ".join(msgs)
+
+
+def publish_status(device) -> None:
+    """Queues, on the current stream, a 4-byte copy of the device status word into a pinned host mirror.  No
+    synchronisation: the mirror shows the word as of the last copy that has completed, and every operator call looks
+    at it first (see ``_raise_if_flagged``).  The autograd functions and ``train_step`` call this once per backward
+    pass / step, so a kernel that flagged a problem (above all a timed-out pipeline wait, after which the kernels skip
+    their work) makes the next call raise instead of returning uninitialised memory."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    m = _status_mirrors.get(idx)
+    if m is None:
+        m = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_mirrors[idx] = m
+    m.copy_(_status_word(torch.device("cuda", idx)), non_blocking=True)
+
+
+def _raise_if_flagged(dev: torch.device) -> None:
+    """Host-side look at the pinned mirror (no synchronisation).  Invalid-result bits raise and are cleared on both
+    sides; an out-of-range index alone is left for ``check_status`` (the slot was skipped, results are defined)."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    m = _status_mirrors.get(idx)
+    if m is None:
+        return
+    v = int(m[0])
+    if v & (_lib.STATUS_PIPELINE_TIMEOUT | _lib.STATUS_INTERNAL):
+        m.zero_()
+        _status_words[idx].zero_()
+        raise RuntimeError(_status_text(idx, v))
 
 
 def check_status(device=None) -> None:
@@ -98,14 +142,10 @@ def check_status(device=None) -> None:
         v = int(w.item())
         if v:
             w.zero_()
-            msgs = []
-            if v & _lib.STATUS_INDEX_OUT_OF_RANGE:
-                msgs.append("an Ind value outside [0, T) was met (slot skipped)")
-            if v & _lib.STATUS_PIPELINE_TIMEOUT:
-                msgs.append("a bounded wait inside a tensor-core kernel ran out (results invalid)")
-            if v & _lib.STATUS_INTERNAL:
-                msgs.append("a tensor-core kernel found its shared memory misaligned and did no work (results invalid)")
-            raise RuntimeError(f"egs kernels on cuda:{idx} reported: " + "; ".join(msgs))
+            m = _status_mirrors.get(idx)
+            if m is not None:
+                m.zero_()
+            raise RuntimeError(_status_text(idx, v))
 
 
 _side_streams: dict[int, "torch.cuda.Stream"] = {}
@@ -160,6 +200,7 @@ def _require_cuda(*tensors) -> torch.device:
             raise RuntimeError("expert gather/scatter kernels need CUDA tensors (there is no CPU path)")
         if t.device != dev:
             raise RuntimeError("all tensors must be on the same CUDA device")
+    _raise_if_flagged(dev)
     return dev
 
 
@@ -249,9 +290,10 @@ def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=
 
 
 def fused_pair_eligible(C1: int, N1: int, N2: int, dtype: torch.dtype, *, w_layout="cn", precision=None) -> bool:
-    """True when :func:`gather_scatter_pair` has a kernel for this shape on the current device (float32, the
-    middle width a multiple of 32 and at most 256, the output width within one tile, tiles fitting in shared memory)."""
-    if dtype != torch.float32 or _state["path"] == "generic":
+    """True when :func:`gather_scatter_pair` has a kernel for this shape on the current device.  float32: the middle
+    width a multiple of 32 and at most 256, the output width within one tile, tiles fitting in shared memory.
+    16-bit: the middle width a multiple of 16 and at most 256, the other widths multiples of 8."""
+    if dtype not in (torch.float32, torch.bfloat16, torch.float16) or _state["path"] == "generic":
         return False
     lib = _lib.load()
     prec, _ = _enums(precision, None)
@@ -260,14 +302,21 @@ def fused_pair_eligible(C1: int, N1: int, N2: int, dtype: torch.dtype, *, w_layo
 
 
 def fused_pair_preferred(X: torch.Tensor, Wg: torch.Tensor, Ind: torch.Tensor) -> bool:
-    """Whether gather -> scatter over these tensors should run as the fused kernel: float32, a shape the kernel
-    takes in both weight layouts, and a grid of at most one wave (one CTA per (expert, 128 expert rows) and per SM;
-    beyond that the two separate kernels, which fit two CTAs per SM, measured faster)."""
-    if X.dtype != torch.float32 or not X.is_cuda:
+    """Whether gather -> scatter over these tensors should run as the fused kernel by default.
+
+    float32: a shape the kernel takes in both weight layouts and a grid of at most one wave (one CTA per (expert, 128
+    expert rows) and per SM; beyond that the two separate kernels, which fit two CTAs per SM, measured faster).
+    16-bit: never by default.  The persistent 16-bit pair kernel is correct and saves the round trip of the middle
+    tensor, but both it and the separate kernels are bound by the bytes the SMs pull from L2 per 128-row tile, and
+    the separate gather kernel halves those with 256-row tiles: whole steps measured 2 % faster to 14 % slower with
+    the fused kernel (B200, bf16 configurations).  ``gather_scatter_pair`` runs it on request."""
+    if not X.is_cuda or X.dtype != torch.float32:
         return False
     I, J = X.shape[2], Wg.shape[2]
     pair_ctas = Wg.shape[0] * ((X.shape[0] * Ind.shape[2] + 127) // 128)
-    return (pair_ctas <= _SM_COUNT and fused_pair_eligible(I, J, I, X.dtype, w_layout="cn")
+    if pair_ctas > _SM_COUNT:
+        return False
+    return (fused_pair_eligible(I, J, I, X.dtype, w_layout="cn")
             and fused_pair_eligible(I, J, I, X.dtype, w_layout="nc"))
 
 
@@ -304,8 +353,11 @@ def gather_scatter_pair(Src, W1, W2, Ind, *, w_layout="cn", out=None, precision=
             if tuple(out.shape) != (B, T, N2) or out.dtype != Src.dtype or not out.is_contiguous():
                 raise ValueError("out must be a contiguous [B,T,N2] tensor of Src's dtype")
             zero = 0
+        ws_bytes = int(lib.egs_scatter_workspace_bytes(B, T, N2, dt))
+        ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if ws_bytes else None
         rc = lib.egs_gather_scatter_pair(Sc.data_ptr(), W1c.data_ptr(), W2c.data_ptr(), Ic.data_ptr(), Mid.data_ptr(),
                                          out.data_ptr(), B, T, E, K, C1, N1, N2, wl, zero, dt, it, prec,
+                                         ws.data_ptr() if ws is not None else None, ws_bytes,
                                          _status_word(dev).data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "egs_gather_scatter_pair")
     if _state["debug"]:

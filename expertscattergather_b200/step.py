@@ -106,23 +106,26 @@ def train_step(X: torch.Tensor, Wg: torch.Tensor, Ws: torch.Tensor, Ind: torch.T
     # float32 outputs are zero-filled ahead of time on the fill stream; 16-bit outputs are initialised by the scatter's
     # own planning step (prefilling them measured slower where the scatter sums in float32 rows)
     prefill = X.dtype == torch.float32
-    fused = fused_pairs and prefill and takes_fused_pairs(X, Wg, Ind)
+    fused = fused_pairs and takes_fused_pairs(X, Wg, Ind)
     Out = dX = None
     dWs0 = dWg0 = None
     if prefill:
         Out, dX, out_filled, fills_done, (dWs0, dWg0) = _prefilled_outputs(
             X, T, Ws.shape[2], main, dw_shapes=(tuple(Ws.shape), tuple(Wg.shape)))
     if fused:
-        # float32 shapes the fused pair kernel takes: two kernels on the critical chain instead of four
-        main.wait_event(out_filled)
+        # shapes the fused pair kernels take: two kernels on the critical chain instead of four
+        if prefill:
+            main.wait_event(out_filled)
         Y, Out = ops.gather_scatter_pair(X, Wg, Ws, Ind, w_layout="cn", out=Out)      # gather + scatter forward
         fwd_done = main.record_event()
         with torch.cuda.stream(side):
             side.wait_event(fwd_done)
-            side.wait_event(fills_done)
+            if prefill:
+                side.wait_event(fills_done)
             dWs = ops.dweight(G, Y, Ind, out_layout="direct_rows", zeroed_out=dWs0)  # scatter backward: dW_s
             dWs.record_stream(main)
-        main.wait_event(fills_done)
+        if prefill:
+            main.wait_event(fills_done)
         dY, dX = ops.gather_scatter_pair(G, Ws, Wg, Ind, w_layout="nc", out=dX)       # dY and dX
         dy_ready = main.record_event()
         with torch.cuda.stream(side):

@@ -138,8 +138,9 @@ size_t egs_dw_workspace_bytes(int64_t E, int64_t FG, int64_t FD, int dtype);
  * synchronise the device or fail on a fragmented heap.  Same operator and arguments as egs_dweight, minus the
  * workspace: the float32 scratch is a 16 MiB array built into the library image (every GPU that loads the
  * library carries it until the process exits).  The entry point itself allocates nothing and frees nothing.
- *   - Limit: E*FG*FD <= egs_static_scratch_max_elements() (4 Mi elements); larger problems return
- *     EGS_ERR_TOO_LARGE with an explanatory egs_last_cuda_error() text and launch nothing.
+ *   - Limit: E*FG*FD <= egs_static_scratch_max_elements() (4 Mi elements) for 16-bit tensors; larger problems return
+ *     EGS_ERR_TOO_LARGE with an explanatory egs_last_cuda_error() text and launch nothing.  float32 tensors
+ *     accumulate straight into `out`, never touch the scratch and are not limited.
  *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with
  *     that device current); make that first call outside any stream capture.
  *   - All calls share the one array, and it keeps whatever the previous call left.  Each call clears what
@@ -153,24 +154,29 @@ int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* I
 /* Capacity of the built-in scratch in float32 elements.  No counterpart in the reference. */
 size_t egs_static_scratch_max_elements(void);
 
-/* Fused pair G -> S in ONE kernel (float32 tensors, tensor-core path only):
+/* Fused pair G -> S in ONE kernel (tensor-core path only):
  *     Mid[slot rows, N1]  = gather(Src)[slot rows, C1] x W1[e]          (overwritten; what egs_gather_gemm computes)
  *     Dst[token rows, N2] += Mid x W2[e]                                 (what egs_gemm_scatter computes)
- * The 128 x N1 tile of Mid stays on the SM between the two contractions; it is also stored, because the backward
- * pass and the weight gradients read it.  Both weights are given in the same layout:
+ * The 128 x N1 tile of Mid stays on the SM between the two contractions (shared memory for float32 tensors, tensor
+ * memory for 16-bit ones); it is also stored, because the backward pass and the weight gradients read it.  Both
+ * weights are given in the same layout:
  *   forward  (egs/triton_kernels.py:382-390 followed by :464-472): Src = X, W1 = W_g [E,I,J], W2 = W_s [E,J,I],
  *            w_layout = EGS_W_CN, C1 = I, N1 = J, N2 = I  ->  Mid = Y, Dst = Out
  *   backward (egs/triton_kernels.py:500-508 followed by :416-424): Src = dOut, W1 = W_s [E,J,I], W2 = W_g [E,I,J],
  *            w_layout = EGS_W_NC, C1 = I, N1 = J, N2 = I  ->  Mid = dY, Dst = dX
  * The reference launches the two kernels of each pair separately; results equal those of the two separate calls
- * up to the order of the float32 additions into Dst.  zero_output as in egs_gemm_scatter.
+ * up to the order of the additions into Dst.  zero_output as in egs_gemm_scatter.
+ * 16-bit tensors run a persistent kernel in which the tensor core works on the gather contraction of the next 128 rows
+ * while the additions of the current ones drain; they need egs_scatter_workspace_bytes(B, T, N2, dtype) bytes of
+ * scratch in workspace (used exactly as egs_gemm_scatter uses it); float32 tensors need none (NULL, 0).
  * Returns EGS_ERR_UNSUPPORTED when egs_fused_pair_eligible says 0: the caller then makes the two separate calls. */
 int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, const void* Ind, void* Mid, void* Dst,
                             int64_t B, int64_t T, int64_t E, int64_t K, int64_t C1, int64_t N1, int64_t N2,
                             int w_layout, int zero_output, int dtype, int index_dtype, int precision,
-                            int32_t* status_word, void* cuda_stream);
-/* 1 if egs_gather_scatter_pair takes this shape on the current device: float32, sm_100, N1 a multiple of 32 and
- * <= 256, N2 within one tile (128 strict / 256 TF32), 16-byte row pitches, and the tiles fit in shared memory. */
+                            void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
+/* 1 if egs_gather_scatter_pair takes this shape on the current device (sm_100, 16-byte row pitches, tiles fit on the SM).
+ * float32: N1 a multiple of 32 and <= 256, N2 within one tile (128 strict / 256 TF32).
+ * 16-bit:  N1 a multiple of 16 and <= 256, C1 and N2 multiples of 8. */
 int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision);
 
 /* Self-test of the kernels' bounded waits (no reference counterpart).  Launches one CTA that waits, with a limit of
