@@ -204,19 +204,22 @@ def run_reference_arm(args, name, passes):
 # -------------------------------------------------------------------------------------------------------------
 # GPU arm
 # -------------------------------------------------------------------------------------------------------------
-def op_work(w, B, U, op):
-    """Algorithmic (flops, bytes) of one operator launch group."""
+def op_work(w, B, U, op, dense_write=True):
+    """Algorithmic (flops, bytes) of one operator launch group.  dense_write=False: the scatter adds into a given,
+    already filled output, so instead of the dense [B,T,I] write only the U touched rows are read and written (the fill
+    is accounted for in its own `fill_out` row)."""
     s = torch.empty((), dtype=w.dtype).element_size()
     N = B * w.E * w.K
     WB = w.E * w.I * w.J * s
     fl = 2 * N * w.I * w.J
     if op in ("gather_fwd", "scatter_bwd_dY"):
         return fl, U * w.I * s + WB + 8 * N + N * w.J * s
+    out_bytes = B * w.T * w.I * s if dense_write else 2 * U * w.I * s
     if op in ("scatter_fwd", "gather_bwd_dX"):
-        return fl, N * w.J * s + WB + 8 * N + B * w.T * w.I * s
+        return fl, N * w.J * s + WB + 8 * N + out_bytes
     if op in ("pair_fwd", "pair_bwd"):
         # fused G -> S: token rows read once, both weights, the middle tensor written once, the output written once
-        return 2 * fl, U * w.I * s + 2 * WB + 8 * N + N * w.J * s + B * w.T * w.I * s
+        return 2 * fl, U * w.I * s + 2 * WB + 8 * N + N * w.J * s + out_bytes
     if op == "fill_out":
         return 0, B * w.T * w.I * s
     return fl, U * w.I * s + N * w.J * s + 8 * N + WB      # dW_g, dW_s
@@ -399,7 +402,7 @@ def operator_breakdown(runner, peaks, reps):
         calls["fill_out"] = lambda: ops.fill_zero(out_buf)
         for op, fn in calls.items():
             ms = time_call(fn, reps, runner.flush_buf)
-            fl, by = op_work(w, b, U, op)
+            fl, by = op_work(w, b, U, op, dense_write=False)
             t_hbm = by / (peaks["hbm_gbs"] * 1e9)
             t_tc = fl * (3 if (w.dtype == torch.float32 and strict) else 1) / (tc * 1e12)
             bound = "hbm" if t_hbm >= t_tc else "tensor"

@@ -25,11 +25,18 @@ EXPORTS = (
     "egs_version", "egs_status_string", "egs_last_cuda_error", "egs_gather_gemm", "egs_gemm_scatter",
     "egs_dweight", "egs_dweight_static_scratch", "egs_static_scratch_max_elements", "egs_dw_workspace_bytes", "egs_scatter_workspace_bytes", "egs_tensor_path_eligible", "egs_fill_zero", "egs_launch_count",
     "egs_gather_scatter_pair", "egs_fused_pair_eligible", "egs_dweight_prezeroed", "egs_selftest_wait_timeout",
+    "egs_describe_plan", "egs_gather_gemm_bias", "egs_gemm_scatter_bias", "egs_route_topk", "egs_index_csr",
+    "egs_index_csr_scratch_bytes", "egs_index_compact", "egs_gemm_scatter_prepared", "egs_gemm_scatter_csr",
 )
 
 
 class Dims(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in ("B", "T", "E", "K", "C", "N")]
+
+
+class PlanInfo(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("tensor_path", "tile_n", "stages", "row_tiles", "persistent", "bulk_epilogue",
+                                            "expert_fastest", "splits", "rows_per_split")]
 
 
 _lock = threading.Lock()
@@ -48,6 +55,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_gather_gemm.argtypes = [vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, vp, vp]
     lib.egs_gemm_scatter.restype = i
     lib.egs_gemm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, i, vp, sz, vp, vp]
+    lib.egs_gather_gemm_bias.restype = i
+    lib.egs_gather_gemm_bias.argtypes = [vp, vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, vp, vp]
+    lib.egs_gemm_scatter_bias.restype = i
+    lib.egs_gemm_scatter_bias.argtypes = [vp, vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, i, vp, sz, vp, vp]
     lib.egs_scatter_workspace_bytes.restype = sz
     lib.egs_scatter_workspace_bytes.argtypes = [i64, i64, i64, i]
     lib.egs_dweight.restype = i
@@ -64,6 +75,20 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.egs_dw_workspace_bytes.argtypes = [i64, i64, i64, i]
     lib.egs_tensor_path_eligible.restype = i
     lib.egs_tensor_path_eligible.argtypes = [i, ctypes.POINTER(Dims), i, ctypes.POINTER(vp), i]
+    lib.egs_route_topk.restype = i
+    lib.egs_route_topk.argtypes = [vp, vp, i64, i64, i64, i64, i, vp]
+    lib.egs_index_csr_scratch_bytes.restype = sz
+    lib.egs_index_csr_scratch_bytes.argtypes = [i64, i64]
+    lib.egs_index_csr.restype = i
+    lib.egs_index_csr.argtypes = [vp, i, i64, i64, i64, i64, vp, vp, vp, vp, vp, sz, vp]
+    lib.egs_index_compact.restype = i
+    lib.egs_index_compact.argtypes = [vp, i, i64, i64, vp, i, vp, vp]
+    lib.egs_gemm_scatter_prepared.restype = i
+    lib.egs_gemm_scatter_prepared.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, i, i, i, vp, sz, vp, vp]
+    lib.egs_gemm_scatter_csr.restype = i
+    lib.egs_gemm_scatter_csr.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(Dims), i, i, i, vp]
+    lib.egs_describe_plan.restype = i
+    lib.egs_describe_plan.argtypes = [i, ctypes.POINTER(Dims), i, i, i, ctypes.POINTER(PlanInfo)]
     lib.egs_fill_zero.restype = i
     lib.egs_fill_zero.argtypes = [vp, sz, vp]
     lib.egs_launch_count.restype = i64

@@ -54,6 +54,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 constexpr long long kInt32Max = 2147483647LL;
 // 16-bit scatter adds directly into the output while no token row receives more contributions than this.
 constexpr int kDirect16Limit = 32;
+// Longest contraction strict float32 runs on the tensor cores under EGS_PATH_AUTO (see run_rowgemm).
+constexpr long long kStrictMaxContraction = 512;
 
 bool device_is_sm100() {
   static thread_local int cached_dev = -1;
@@ -85,9 +87,16 @@ int check_dims(const egs_dims* d) {
   return EGS_OK;
 }
 
-int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, void* Out, const egs_dims* dims,
+// Grid order of the row kernels (see their comment).  Token rows touched: X rows for G, the (float32) rows added to for S.
+int pick_expert_fastest(const egs_dims& d, bool scatter, int dtype) {
+  const double act_bytes = static_cast<double>(d.B) * d.T * (scatter ? d.N * 4.0 : d.C * static_cast<double>(elem_size(dtype)));
+  const double w_bytes = static_cast<double>(d.E) * d.C * d.N * elem_size(dtype);
+  return (act_bytes > 96e6 && w_bytes < 64e6 && (d.B * d.K + 127) / 128 <= 65535) ? 1 : 0;
+}
+
+int run_rowgemm(bool scatter, const void* A, const void* W, const void* bias, const void* Ind, void* Out, const egs_dims* dims,
                 int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path, void* workspace,
-                size_t workspace_bytes, int32_t* status, void* stream) {
+                size_t workspace_bytes, int32_t* status, void* stream, const int* csr_info = nullptr) {
   if (int rc = check_dims(dims)) return rc;
   if (!valid_dtype(dtype) || !valid_index(index_dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
       (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32) ||
@@ -111,7 +120,12 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   int* plan = nullptr;
   const bool eligible = device_is_sm100() && rowgemm_tensor_ok(d, dtype, A, W, Out);
   if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
-  const bool tensor = (path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible);
+  // Strict float32 on long contractions: the tensor core's accumulator additions truncate, and the error grows with the
+  // contraction length (3.3e-5 of max|ref| at C = 4096 against the 1e-5 bar).  EGS_PATH_AUTO therefore keeps strict
+  // float32 on the tensor cores only up to kStrictMaxContraction and takes the FFMA kernels beyond.
+  const bool strict_long = (dtype == EGS_F32 && precision == EGS_PREC_STRICT && d.C > kStrictMaxContraction);
+  const bool tensor = ((path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible && !strict_long)) && !(d.C == 0) &&
+                      (bias == nullptr || aligned16(bias));
   if (f32_rows) {
     const size_t need = egs_scatter_workspace_bytes(d.B, d.T, d.N, dtype);
     if (!workspace || workspace_bytes < need || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
@@ -122,10 +136,14 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     cudaError_t err;
     if (tensor && !no_work && d.C > 0) {
       plan = reinterpret_cast<int*>(ws);
-      err = launch_fill_zero(ws, 256 + counter_bytes, st);
-      if (err == cudaSuccess)
-        err = launch_scatter_plan(Ind, index_dtype, static_cast<int>(d.B), static_cast<int>(d.T), static_cast<int>(d.E),
-                                  static_cast<int>(d.K), counters, plan, kDirect16Limit, status, st);
+      if (csr_info) {   // a CSR of this Ind has been built: its heaviest-row figure decides, no pass over Ind
+        err = launch_plan_from_info(csr_info, kDirect16Limit, plan, status, st);
+      } else {
+        err = launch_fill_zero(ws, 256 + counter_bytes, st);
+        if (err == cudaSuccess)
+          err = launch_scatter_plan(Ind, index_dtype, static_cast<int>(d.B), static_cast<int>(d.T), static_cast<int>(d.E),
+                                    static_cast<int>(d.K), counters, plan, kDirect16Limit, status, st);
+      }
       if (err == cudaSuccess) err = launch_scatter_init(plan, acc, Out, n_out, zero_output, dtype, st);
     } else {
       err = zero_output ? launch_fill_zero(acc, n_out * sizeof(float), st) : launch_convert_to_f32(Out, acc, n_out, dtype, st);
@@ -142,7 +160,7 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
     return err == cudaSuccess ? EGS_OK : fail_cuda(err, "scatter scratch convert");
   };
   if (no_work) return finish_rows();
-  if (d.C == 0) {   // empty contraction: gather output is all zeros, scatter adds nothing
+  if (d.C == 0 && bias == nullptr) {   // empty contraction: gather output is all zeros, scatter adds nothing
     if (!scatter) {
       cudaError_t err = launch_fill_zero(Out, out_bytes, st);
       if (err != cudaSuccess) return fail_cuda(err, "fill_zero");
@@ -151,7 +169,7 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
   }
 
   RowGemmParams p{};
-  p.A = A; p.W = W; p.Ind = Ind; p.Out = Out; p.acc = acc; p.plan = plan; p.status = status;
+  p.A = A; p.W = W; p.bias = bias; p.Ind = Ind; p.Out = Out; p.acc = acc; p.plan = plan; p.status = status;
   p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
   p.C = static_cast<int>(d.C); p.N = static_cast<int>(d.N);
   p.M = static_cast<int>(d.B * d.K);
@@ -159,10 +177,7 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* Ind, voi
 
   cudaError_t err;
   if (tensor) {
-    // grid order: see the kernel's comment.  Token rows touched: X rows for G, the (float32) rows added to for S.
-    const double act_bytes = static_cast<double>(d.B) * d.T * (scatter ? d.N * 4.0 : d.C * static_cast<double>(elem_size(dtype)));
-    const double w_bytes = static_cast<double>(d.E) * d.C * d.N * elem_size(dtype);
-    p.expert_fastest = (act_bytes > 96e6 && w_bytes < 64e6 && (d.B * d.K + 127) / 128 <= 65535) ? 1 : 0;
+    p.expert_fastest = pick_expert_fastest(d, scatter, dtype);
     const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
     err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
   } else {
@@ -199,15 +214,93 @@ int64_t egs_launch_count(void) { return g_launches.load(std::memory_order_relaxe
 
 int egs_gather_gemm(const void* X, const void* W, const void* Ind, void* Y, const egs_dims* dims, int w_layout,
                     int dtype, int index_dtype, int precision, int path, int32_t* status_word, void* cuda_stream) {
-  return run_rowgemm(false, X, W, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, nullptr, 0,
+  return run_rowgemm(false, X, W, nullptr, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, nullptr, 0,
+                     status_word, cuda_stream);
+}
+
+int egs_gather_gemm_bias(const void* X, const void* W, const void* bias, const void* Ind, void* Y, const egs_dims* dims,
+                         int w_layout, int dtype, int index_dtype, int precision, int path, int32_t* status_word,
+                         void* cuda_stream) {
+  return run_rowgemm(false, X, W, bias, Ind, Y, dims, w_layout, 0, dtype, index_dtype, precision, path, nullptr, 0,
                      status_word, cuda_stream);
 }
 
 int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, const egs_dims* dims, int w_layout,
                      int zero_output, int dtype, int index_dtype, int precision, int path, void* workspace,
                      size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
-  return run_rowgemm(true, Y, W, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path, workspace,
+  return run_rowgemm(true, Y, W, nullptr, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path, workspace,
                      workspace_bytes, status_word, cuda_stream);
+}
+
+int egs_gemm_scatter_bias(const void* Y, const void* W, const void* bias, const void* Ind, void* Out, const egs_dims* dims,
+                          int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path,
+                          void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  return run_rowgemm(true, Y, W, bias, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path, workspace,
+                     workspace_bytes, status_word, cuda_stream);
+}
+
+int egs_gemm_scatter_prepared(const void* Y, const void* W, const void* bias, const void* Ind, const int* csr_info, void* Out,
+                              const egs_dims* dims, int w_layout, int zero_output, int dtype, int index_dtype, int precision,
+                              int path, void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream) {
+  return run_rowgemm(true, Y, W, bias, Ind, Out, dims, w_layout, zero_output, dtype, index_dtype, precision, path, workspace,
+                     workspace_bytes, status_word, cuda_stream, csr_info);
+}
+
+int egs_route_topk(const float* scores, void* Ind, int64_t B, int64_t T, int64_t E, int64_t K, int index_dtype, void* cuda_stream) {
+  if (B < 0 || T < 0 || E < 0 || K < 0 || !valid_index(index_dtype)) return EGS_ERR_INVALID_ARGUMENT;
+  if (K > T || K > 1024) return EGS_ERR_UNSUPPORTED;                 // K distinct tokens per expert; the sort buffer holds 1024
+  if (index_dtype == EGS_I16 && T > 32767) return EGS_ERR_TOO_LARGE;
+  if (B * E > kInt32Max || B * T * E > (1LL << 40)) return EGS_ERR_TOO_LARGE;
+  if (B * E * K == 0) return EGS_OK;
+  if (!scores || !Ind) return EGS_ERR_INVALID_ARGUMENT;
+  cudaError_t err = launch_route_topk(scores, Ind, index_dtype, static_cast<int>(B), static_cast<int>(T), static_cast<int>(E),
+                                      static_cast<int>(K), static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "route_topk launch");
+}
+
+size_t egs_index_csr_scratch_bytes(int64_t B, int64_t T) {
+  if (B <= 0 || T <= 0) return 64;
+  return index_csr_scratch_ints(B * T) * sizeof(int);
+}
+
+int egs_index_csr(const void* Ind, int index_dtype, int64_t B, int64_t T, int64_t E, int64_t K, int32_t* counts, int32_t* offsets,
+                  int32_t* entries, int32_t* info, void* scratch, size_t scratch_bytes, void* cuda_stream) {
+  egs_dims d{B, T, E, K, 0, 0};
+  if (int rc = check_dims(&d)) return rc;
+  if (!valid_index(index_dtype) || !offsets || !info) return EGS_ERR_INVALID_ARGUMENT;
+  if (B * T > 0 && !counts) return EGS_ERR_INVALID_ARGUMENT;
+  if (B * E * K > 0 && (!Ind || !entries)) return EGS_ERR_INVALID_ARGUMENT;
+  if (!scratch || scratch_bytes < egs_index_csr_scratch_bytes(B, T)) return EGS_ERR_WORKSPACE;
+  cudaError_t err = launch_index_csr(Ind, index_dtype, static_cast<int>(B), static_cast<int>(T), static_cast<int>(E),
+                                     static_cast<int>(K), counts, offsets, entries, info, static_cast<int*>(scratch),
+                                     static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "index_csr launch");
+}
+
+int egs_index_compact(const void* Ind, int index_dtype, int64_t n, int64_t T, void* out, int out_dtype, int32_t* status_word,
+                      void* cuda_stream) {
+  if (n < 0 || T < 0 || !valid_index(index_dtype) || !valid_index(out_dtype)) return EGS_ERR_INVALID_ARGUMENT;
+  if (out_dtype == EGS_I16 && T > 32767) return EGS_ERR_TOO_LARGE;
+  if (out_dtype == EGS_I32 && T > kInt32Max) return EGS_ERR_TOO_LARGE;
+  if (n == 0) return EGS_OK;
+  if (!Ind || !out) return EGS_ERR_INVALID_ARGUMENT;
+  cudaError_t err = launch_compact_index(Ind, index_dtype, n, T, out, out_dtype, status_word, static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "index_compact launch");
+}
+
+int egs_gemm_scatter_csr(const void* Y, const void* W, const void* bias, const int32_t* offsets, const int32_t* entries, void* Out,
+                         const egs_dims* dims, int w_layout, int accumulate, int dtype, void* cuda_stream) {
+  if (int rc = check_dims(dims)) return rc;
+  if (!valid_dtype(dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC)) return EGS_ERR_INVALID_ARGUMENT;
+  const egs_dims& d = *dims;
+  if (d.B * d.T * d.N == 0) return EGS_OK;
+  if (!Out || !offsets) return EGS_ERR_INVALID_ARGUMENT;
+  if (d.B * d.E * d.K > 0 && (!Y || !W || !entries) && d.C > 0) return EGS_ERR_INVALID_ARGUMENT;
+  if (d.N > 1024 || d.C > 12000) return EGS_ERR_UNSUPPORTED;          // 8 columns per thread; one Y row in shared memory
+  cudaError_t err = launch_csr_scatter(Y, W, bias, offsets, entries, Out, d.B * d.T, static_cast<int>(d.E), static_cast<int>(d.K),
+                                       static_cast<int>(d.C), static_cast<int>(d.N), w_layout, accumulate, dtype,
+                                       static_cast<cudaStream_t>(cuda_stream));
+  return err == cudaSuccess ? EGS_OK : fail_cuda(err, "gemm_scatter_csr launch");
 }
 
 int egs_selftest_wait_timeout(int32_t* status_word, int* out2, int64_t limit_cycles, void* cuda_stream) {
@@ -223,6 +316,7 @@ int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, in
   FusedParams p{};
   p.C1 = static_cast<int>(C1); p.N1 = static_cast<int>(N1); p.N2 = static_cast<int>(N2); p.w_layout = w_layout;
   if (dtype != EGS_F32) return configure_tensor_pair16(p) != 0 ? 1 : 0;
+  if (precision == EGS_PREC_STRICT && C1 > kStrictMaxContraction) return 0;     // see run_rowgemm
   return configure_tensor_fused_pair(p, precision) != 0 ? 1 : 0;
 }
 
@@ -445,6 +539,37 @@ int egs_dweight_static_scratch(const void* Xsrc, const void* Ysrc, const void* I
 }
 
 size_t egs_static_scratch_max_elements(void) { return EGS_STATIC_SCRATCH_FLOATS; }
+
+int egs_describe_plan(int op, const egs_dims* dims, int w_layout, int dtype, int precision, egs_plan_info* out) {
+  if (!out || !dims || op < 0 || op > 2 || !valid_dtype(dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
+      (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32))
+    return EGS_ERR_INVALID_ARGUMENT;
+  if (int rc = check_dims(dims)) return rc;
+  std::memset(out, 0, sizeof(*out));
+  const egs_dims& d = *dims;
+  const int es = elem_size(dtype);
+  out->tensor_path = (device_is_sm100() && (d.C * es) % 16 == 0 && (d.N * es) % 16 == 0) ? 1 : 0;
+  if (op != 2 && dtype == EGS_F32 && precision == EGS_PREC_STRICT && d.C > kStrictMaxContraction) out->tensor_path = 0;
+  if (!out->tensor_path || d.B * d.E * d.K == 0 || d.C == 0 || d.N == 0) return EGS_OK;
+  if (op == 2) {
+    DWeightParams p{};
+    p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
+    p.FG = static_cast<int>(d.C); p.FD = static_cast<int>(d.N); p.M = static_cast<int>(d.B * d.K);
+    configure_tensor_dweight(p, dtype, precision);
+    out->tile_n = p.BN; out->stages = p.stages; out->row_tiles = p.row_tiles; out->splits = p.splits;
+    out->rows_per_split = p.rows_per_split;
+    return EGS_OK;
+  }
+  RowGemmParams p{};
+  p.B = static_cast<int>(d.B); p.T = static_cast<int>(d.T); p.E = static_cast<int>(d.E); p.K = static_cast<int>(d.K);
+  p.C = static_cast<int>(d.C); p.N = static_cast<int>(d.N); p.M = static_cast<int>(d.B * d.K);
+  p.w_layout = w_layout;
+  p.expert_fastest = pick_expert_fastest(d, op == 1, dtype);
+  configure_tensor_rowgemm(p, op == 1, dtype, precision);
+  out->tile_n = p.BN; out->stages = p.stages; out->row_tiles = p.row_tiles; out->persistent = p.persistent;
+  out->bulk_epilogue = (p.persistent || op == 1) ? p.bulk_epilogue : 0; out->expert_fastest = p.expert_fastest;
+  return EGS_OK;
+}
 
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers, int n_pointers) {
   if (!dims || !valid_dtype(dtype) || op < 0 || op > 2) return 0;

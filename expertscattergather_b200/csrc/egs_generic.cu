@@ -109,11 +109,12 @@ __global__ void __launch_bounds__(NTHREADS) generic_rowgemm_kernel(RowGemmParams
     for (int j = 0; j < 4; ++j) {
       const int nn = n0 + tx * 4 + j;
       if (nn >= p.N) continue;
+      const float v = acc[i][j] + (p.bias ? to_f32<T>(static_cast<const T*>(p.bias)[static_cast<long long>(e) * p.N + nn]) : 0.f);
       if (SCATTER) {
-        if (sizeof(T) == 2) atomicAdd(p.acc + ro + nn, acc[i][j]);   // 16-bit: float32 accumulation rows
-        else atomicAdd(reinterpret_cast<float*>(Out) + ro + nn, acc[i][j]);
+        if (sizeof(T) == 2) atomicAdd(p.acc + ro + nn, v);   // 16-bit: float32 accumulation rows
+        else atomicAdd(reinterpret_cast<float*>(Out) + ro + nn, v);
       } else {
-        Out[ro + nn] = from_f32<T>(acc[i][j]);
+        Out[ro + nn] = from_f32<T>(v);
       }
     }
   }

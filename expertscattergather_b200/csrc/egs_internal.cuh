@@ -47,6 +47,8 @@ struct RowGemmParams {
   float* acc;         // S with 16-bit tensors: float32 accumulation rows [B*T, N]; otherwise unused
   const int* plan;    // S with 16-bit tensors: device flag, non-zero = accumulate in the float32 rows,
                       // zero = add directly into the 16-bit output; NULL = always the float32 rows
+  const void* bias;   // optional [E, N] in the tensors' dtype: bias[e, :] is added to every produced row of expert e
+                      // (G: to the stored row; S: to the row before it is added to its token row); NULL = none
   int32_t* status;    // optional device status word
   int B, T, E, K, C, N;
   int M;              // expert rows per expert = B*K
@@ -138,6 +140,19 @@ struct alignas(64) TensorMap3 {
   unsigned char bytes[128];
 };
 bool encode_tensor_map_16bit(TensorMap3* out, const void* base, const unsigned long long dims[3], const unsigned box[3]);
+
+// Index preparation (egs_index.cu).  All index arrays are int32 on the device.
+cudaError_t launch_route_topk(const float* scores, void* ind, int index_dtype, int B, int T, int E, int K, cudaStream_t st);
+size_t index_csr_scratch_ints(long long rows);
+cudaError_t launch_index_csr(const void* ind, int index_dtype, int B, int T, int E, int K, int* counts, int* offsets, int* entries,
+                             int* info, int* scratch, cudaStream_t st);
+cudaError_t launch_compact_index(const void* ind, int index_dtype, long long n, long long T, void* out, int out_dtype,
+                                 int32_t* status, cudaStream_t st);
+cudaError_t launch_csr_scatter(const void* Y, const void* W, const void* bias, const int* offsets, const int* entries, void* Out,
+                               long long rows, int E, int K, int C, int N, int w_layout, int accumulate, int dtype,
+                               cudaStream_t st);
+// *plan = (info[0] > limit): the 16-bit scatter's choice taken from a prepared CSR instead of a pass over Ind
+cudaError_t launch_plan_from_info(const int* info, int limit, int* plan, int32_t* status, cudaStream_t st);
 
 // Bounded-wait self-test (see the kernel): out = two ints on the device.
 cudaError_t launch_wait_timeout_selftest(int32_t* status, int* out, long long limit_cycles, cudaStream_t st);

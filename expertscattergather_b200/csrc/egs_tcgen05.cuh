@@ -428,6 +428,15 @@ __device__ __forceinline__ void store4(T* dst, uint32_t x0, uint32_t x1, uint32_
   *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(dst, x0, x1), pack2(dst, x2, x3));
 }
 
+// Adds bias[0..3] (elements of type T, 4 consecutive columns) to four accumulator values held as float bits.
+template <typename T>
+__device__ __forceinline__ void add_bias4(const T* bias, uint32_t& x0, uint32_t& x1, uint32_t& x2, uint32_t& x3) {
+  x0 = __float_as_uint(__uint_as_float(x0) + to_f32<T>(bias[0]));
+  x1 = __float_as_uint(__uint_as_float(x1) + to_f32<T>(bias[1]));
+  x2 = __float_as_uint(__uint_as_float(x2) + to_f32<T>(bias[2]));
+  x3 = __float_as_uint(__uint_as_float(x3) + to_f32<T>(bias[3]));
+}
+
 __device__ __forceinline__ uint32_t tmem_cols_for(int bn) {
   uint32_t c = 32;
   while (c < static_cast<uint32_t>(bn)) c <<= 1;

@@ -414,7 +414,8 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
       // direct 16-bit adds as bulk reductions: every lane stages 128 bytes (64 columns) of its own row in the idle
       // ring and hands them to the copy engine (see the persistent variant)
       static_assert(2u * kBulkBufBytes <= 16384u, "two staging buffers per warp");
-      const bool bulk16 = direct16 && p.bulk_epilogue && (pp.stages * pp.stage_bytes >= 8u * 2u * kBulkBufBytes);
+      const bool bulk16 = direct16 && p.bulk_epilogue && p.bias == nullptr && (pp.stages * pp.stage_bytes >= 8u * 2u * kBulkBufBytes);
+      const T* bias_row = p.bias ? static_cast<const T*>(p.bias) + static_cast<long long>(e) * p.N : nullptr;
       if (bulk16) {
         if constexpr (ES == 2 && SCATTER) {
           const uint32_t my_stage = pp.tiles0 + static_cast<uint32_t>(warp) * (2u * kBulkBufBytes) + static_cast<uint32_t>(lane) * kBulkRowPitch;
@@ -458,7 +459,18 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
                               lane, [&](int row, int cj, const uint32_t (&x)[8]) {
                                 const int ro = hdr->row_o[mt * kTileM + lg * 32 + row];
                                 const int col = col0 + cj;
-                                if (ro >= 0 && col < p.N) red8(out + static_cast<long long>(ro) * p.N + col, x);
+                                if (ro >= 0 && col < p.N) {
+                                  if (bias_row) {
+                                    uint32_t y[8];
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) y[i] = x[i];
+                                    add_bias4<T>(bias_row + col, y[0], y[1], y[2], y[3]);
+                                    add_bias4<T>(bias_row + col + 4, y[4], y[5], y[6], y[7]);
+                                    red8(out + static_cast<long long>(ro) * p.N + col, y);
+                                  } else {
+                                    red8(out + static_cast<long long>(ro) * p.N + col, x);
+                                  }
+                                }
                               });
           }
         }
@@ -472,6 +484,7 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_rowgemm_kern
                             const int col = col0 + cj;
                             if (ro >= 0 && col < p.N) {
                               const long long off = static_cast<long long>(ro) * p.N + col;
+                              if (bias_row) add_bias4<T>(bias_row + col, x0, x1, x2, x3);
                               if (SCATTER) {
                                 if (direct16) red4(out + off, x0, x1, x2, x3);
                                 else red4(acc_rows + off, x0, x1, x2, x3);
@@ -777,7 +790,7 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
     // bulk adds (direct 16-bit scatter): every lane stages 128 bytes of its own row and hands them to the copy
     // engine - no transpose, no shuffles, and the warp does not wait on the load/store unit.  (For float32 rows
     // the same scheme needs twice the operations per column and measured slower than the transposed reds.)
-    const bool bulk = direct16 && p.bulk_epilogue;
+    const bool bulk = direct16 && p.bulk_epilogue && p.bias == nullptr;
     const uint32_t my_stage = tile + static_cast<uint32_t>(lane) * kBulkRowPitch;
     int q = 0;                                           // bulk groups committed so far by this thread
     bool alive = true;
@@ -832,6 +845,7 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
                             const int col = col0 + cj;
                             if (ro >= 0 && col < p.N) {
                               const long long off = static_cast<long long>(ro) * p.N + col;
+                              if (p.bias) add_bias4<T>(static_cast<const T*>(p.bias) + static_cast<long long>(blk.e) * p.N + col, x0, x1, x2, x3);
                               if (SCATTER) {
                                 if (direct16) red4(out + off, x0, x1, x2, x3);
                                 else red4(acc_rows + off, x0, x1, x2, x3);
@@ -1648,7 +1662,12 @@ size_t configure_tensor_dweight(DWeightParams& p, int dtype, int precision) {
   const long long tiles = static_cast<long long>((p.FG + f_tile - 1) / f_tile) * ((p.FD + bn - 1) / bn) * p.E;
   // as many row ranges as still fit in one wave of CTAs (two CTAs per SM with 128-feature tiles)
   long long want = (static_cast<long long>(kSmCount) * (p.row_tiles == 2 ? 1 : 2)) / tiles;
-  const long long min_splits = (p.M + kMaxRowsPerSplit - 1) / kMaxRowsPerSplit;
+  // Strict float32: the tensor core adds every product group into the float32 accumulator with truncation, an error that
+  // grows with the number of accumulation steps (measured 1.5e-5 of max|ref| after 8192 contraction rows, against a
+  // 1e-5 bar).  Ranges of at most 1024 rows keep it near 3e-6; the partial tiles are then summed by float32 atomics,
+  // which round correctly.
+  const int max_rows = strict ? 1024 : kMaxRowsPerSplit;
+  const long long min_splits = (p.M + max_rows - 1) / max_rows;
   if (want < min_splits) want = min_splits;
   const long long max_splits = (p.M + kr - 1) / kr;
   if (want > max_splits) want = max_splits;

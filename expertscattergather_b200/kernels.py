@@ -20,7 +20,8 @@ import torch
 
 from . import ops
 
-__all__ = ["create_kernels", "ExpertGatherFunction", "ExpertScatterFunction", "ExpertGatherScatterFunction", "dtype_to_type_id",
+__all__ = ["create_kernels", "ExpertGatherFunction", "ExpertScatterFunction", "ExpertGatherScatterFunction",
+           "ExpertGatherBiasFunction", "ExpertScatterBiasFunction", "dtype_to_type_id",
            "expert_gather_forward_call", "expert_gather_backward_call", "expert_scatter_forward_call",
            "expert_scatter_backward_call", "OP_NAMESPACE"]
 
@@ -202,6 +203,58 @@ class ExpertScatterFunction(torch.autograd.Function):
         grad_Y = ops.gather_gemm(grad_X, W, Ind, w_layout="nc") if need_y else None
         grad_W = ops.dweight(grad_X, Y, Ind, out_layout="direct_rows") if need_w else None
         return grad_Y, grad_W, None, None, None
+
+
+class ExpertGatherBiasFunction(torch.autograd.Function):
+    """``ExpertGatherFunction`` with the per-expert bias of ``ExpertGather(bias=True)`` added in the kernel's epilogue:
+    ``Y[b,e,k,:] = X[b, Ind[b,e,k], :] @ W[e] + bias[e]`` with bias [E,1,J] - what the reference computes as
+    ``ExpertGatherFunction.apply(...) + self.bias`` (``egs/torch_interface.py:54-56``).  ``apply(X, W, bias, Ind)``;
+    backward returns ``(grad_X, grad_W, grad_bias, None)``, grad_bias = the sum of grad_output over batch and slot."""
+
+    @staticmethod
+    def forward(ctx, X, W, bias, Ind):
+        ctx.save_for_backward(X, W, Ind)
+        ctx.bias_shape = tuple(bias.shape)
+        return ops.gather_gemm(X, W, Ind, w_layout="cn", bias=bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        X, W, Ind = ctx.saved_tensors
+        need_x, need_w, need_b = ctx.needs_input_grad[:3]
+        grad_output = grad_output.contiguous()
+        grad_W = _weight_grad_on_side_stream(X, grad_output, Ind, "gathered_rows") if need_w else None
+        grad_X = ops.gemm_scatter(grad_output, W, Ind, X.shape[1], w_layout="nc") if need_x else None
+        grad_b = grad_output.sum(dim=(0, 2)).reshape(ctx.bias_shape) if need_b else None
+        _join_side(grad_output)
+        return grad_X, grad_W, grad_b, None
+
+
+class ExpertScatterBiasFunction(torch.autograd.Function):
+    """``ExpertScatterFunction`` with a per-expert bias added to every routed slot's product before it is scattered:
+    ``Out[b,t,:] = sum over slots (e,k) routed to t of (Y[b,e,k,:] @ W[e] + bias[e])`` with bias [E,1,I], fused into the
+    scatter's epilogue.  ``apply(Y, W, bias, Ind, T)``; backward returns ``(grad_Y, grad_W, grad_bias, None, None)``.
+    grad_bias[e] is the sum over the slots of expert e of the gathered rows of grad_Out - operator D against a tensor of
+    ones, so no [B,E,K,I] gather is materialised."""
+
+    @staticmethod
+    def forward(ctx, Y, W, bias, Ind, T):
+        ctx.save_for_backward(Y, W, Ind)
+        ctx.bias_shape = tuple(bias.shape)
+        return ops.gemm_scatter(Y, W, Ind, int(T), w_layout="cn", bias=bias)
+
+    @staticmethod
+    def backward(ctx, grad_X):
+        Y, W, Ind = ctx.saved_tensors
+        need_y, need_w, need_b = ctx.needs_input_grad[:3]
+        grad_X = grad_X.contiguous()
+        grad_W = _weight_grad_on_side_stream(grad_X, Y, Ind, "direct_rows") if need_w else None
+        grad_Y = ops.gather_gemm(grad_X, W, Ind, w_layout="nc") if need_y else None
+        grad_b = None
+        if need_b:
+            ones = torch.ones(Y.shape[0], Y.shape[1], Y.shape[2], 8, device=Y.device, dtype=Y.dtype)
+            grad_b = ops.dweight(grad_X, ones, Ind, out_layout="gathered_rows")[:, :, 0].reshape(ctx.bias_shape)
+        _join_side(grad_X)
+        return grad_Y, grad_W, grad_b, None, None
 
 
 class ExpertGatherScatterFunction(torch.autograd.Function):

@@ -14,7 +14,7 @@ import torch
 from . import _lib
 
 __all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eligible", "fused_pair_preferred", "dweight", "fill_zero", "side_stream", "fill_stream", "set_precision", "get_precision", "set_path", "get_path",
-           "check_status", "reset_status", "publish_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible"]
+           "check_status", "reset_status", "publish_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible", "describe_plan", "route_topk", "build_index_csr", "compact_index", "gemm_scatter_csr", "IndexCSR"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
 _PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR}
@@ -222,9 +222,21 @@ def _w_dims(W: torch.Tensor, w_layout: str):
     raise ValueError("w_layout must be 'cn' ([E,C,N]) or 'nc' ([E,N,C])")
 
 
-def gather_gemm(X, W, Ind, *, w_layout="cn", precision=None, path=None):
-    """Operator G: ``Y[b,e,k,:] = X[b, Ind[b,e,k], :] @ Wv[e]`` with ``Wv = W`` ('cn', W is [E,C,N]) or
-    ``W^T`` per expert ('nc', W is [E,N,C]).  X [B,T,C] -> Y [B,E,K,N], dtype of X."""
+def _bias_rows(bias, E, N, dtype, dev):
+    """A per-expert bias given as [E, N] or [E, 1, N] -> contiguous [E, N] of the tensors' dtype (None stays None)."""
+    if bias is None:
+        return None
+    if bias.numel() != E * N or bias.shape[0] != E or bias.shape[-1] != N:
+        raise ValueError(f"bias must be [E, N] or [E, 1, N] = [{E}, {N}], got {tuple(bias.shape)}")
+    if not bias.is_cuda or bias.device != dev:
+        raise RuntimeError("bias must be on the tensors' CUDA device")
+    return bias.reshape(E, N).to(dtype).contiguous()
+
+
+def gather_gemm(X, W, Ind, *, w_layout="cn", precision=None, path=None, bias=None):
+    """Operator G: ``Y[b,e,k,:] = X[b, Ind[b,e,k], :] @ Wv[e] (+ bias[e])`` with ``Wv = W`` ('cn', W is [E,C,N]) or
+    ``W^T`` per expert ('nc', W is [E,N,C]).  X [B,T,C] -> Y [B,E,K,N], dtype of X.  ``bias`` ([E,N] or [E,1,N]) is
+    added in the kernel's epilogue."""
     lib = _lib.load()
     if X.dim() != 3 or W.dim() != 3 or Ind.dim() != 3:
         raise ValueError("expected X[B,T,C], W[E,.,.], Ind[B,E,K]")
@@ -243,17 +255,26 @@ def gather_gemm(X, W, Ind, *, w_layout="cn", precision=None, path=None):
     with torch.cuda.device(dev):
         Y = torch.empty((B, E, K, N), device=dev, dtype=X.dtype)
         dims = _lib.Dims(B, T, E, K, C, N)
-        rc = lib.egs_gather_gemm(Xc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), Y.data_ptr(), ctypes.byref(dims), wl, dt,
-                                 it, prec, pth, _status_word(dev).data_ptr(), _stream_ptr(dev))
+        bias_c = _bias_rows(bias, E, N, X.dtype, dev)
+        if bias_c is None:
+            rc = lib.egs_gather_gemm(Xc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), Y.data_ptr(), ctypes.byref(dims), wl, dt,
+                                     it, prec, pth, _status_word(dev).data_ptr(), _stream_ptr(dev))
+        else:
+            rc = lib.egs_gather_gemm_bias(Xc.data_ptr(), Wc.data_ptr(), bias_c.data_ptr(), Ic.data_ptr(), Y.data_ptr(),
+                                          ctypes.byref(dims), wl, dt, it, prec, pth, _status_word(dev).data_ptr(),
+                                          _stream_ptr(dev))
     _lib.check(rc, "egs_gather_gemm")
     if _state["debug"]:
         check_status(dev)
     return Y
 
 
-def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=None):
-    """Operator S: ``Out[b, Ind[b,e,k], :] += Y[b,e,k,:] @ Wv[e]``; duplicates accumulate.
-    Y [B,E,K,C] -> Out [B,T,N].  ``out=None`` allocates and zero-fills; a given ``out`` is added to."""
+def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=None, bias=None, csr=None):
+    """Operator S: ``Out[b, Ind[b,e,k], :] += Y[b,e,k,:] @ Wv[e] (+ bias[e])``; duplicates accumulate.
+    Y [B,E,K,C] -> Out [B,T,N].  ``out=None`` allocates and zero-fills; a given ``out`` is added to.  ``bias`` ([E,N] or
+    [E,1,N]) is added to every routed slot's product before it is scattered.  ``csr``: an :class:`IndexCSR` of this
+    ``Ind`` - the 16-bit scatter then takes its choice between direct additions and float32 rows from it instead of
+    counting the contributions per token row again."""
     lib = _lib.load()
     if Y.dim() != 4 or W.dim() != 3 or Ind.dim() != 3:
         raise ValueError("expected Y[B,E,K,C], W[E,.,.], Ind[B,E,K]")
@@ -280,9 +301,23 @@ def gemm_scatter(Y, W, Ind, T, *, w_layout="cn", out=None, precision=None, path=
         dims = _lib.Dims(B, T, E, K, C, N)
         ws_bytes = int(lib.egs_scatter_workspace_bytes(B, T, N, dt))
         ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if ws_bytes else None
-        rc = lib.egs_gemm_scatter(Yc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl,
-                                  zero, dt, it, prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
-                                  _status_word(dev).data_ptr(), _stream_ptr(dev))
+        bias_c = _bias_rows(bias, E, N, Y.dtype, dev)
+        if csr is not None:
+            if (csr.B, csr.T, csr.E, csr.K) != (B, T, E, K):
+                raise ValueError("the CSR was built for another Ind shape or T")
+            rc = lib.egs_gemm_scatter_prepared(Yc.data_ptr(), Wc.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                               Ic.data_ptr(), csr.info.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl, zero,
+                                               dt, it, prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
+                                               _status_word(dev).data_ptr(), _stream_ptr(dev))
+        elif bias_c is None:
+            rc = lib.egs_gemm_scatter(Yc.data_ptr(), Wc.data_ptr(), Ic.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl,
+                                      zero, dt, it, prec, pth, ws.data_ptr() if ws is not None else None, ws_bytes,
+                                      _status_word(dev).data_ptr(), _stream_ptr(dev))
+        else:
+            rc = lib.egs_gemm_scatter_bias(Yc.data_ptr(), Wc.data_ptr(), bias_c.data_ptr(), Ic.data_ptr(), out.data_ptr(),
+                                           ctypes.byref(dims), wl, zero, dt, it, prec, pth,
+                                           ws.data_ptr() if ws is not None else None, ws_bytes,
+                                           _status_word(dev).data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "egs_gemm_scatter")
     if _state["debug"]:
         check_status(dev)
@@ -407,6 +442,128 @@ def dweight(Xsrc, Ysrc, Ind, *, out_layout="gathered_rows", precision=None, path
     _lib.check(rc, "egs_dweight")
     if _state["debug"]:
         check_status(dev)
+    return out
+
+
+def describe_plan(op: str, B, T, E, K, C, N, dtype, *, w_layout="cn", precision=None) -> dict:
+    """The kernel variant 'auto' runs for operator op ('G', 'S' or 'D'; for D pass C = FG, N = FD) at these sizes:
+    dict with tensor_path, tile_n, stages, row_tiles, persistent, bulk_epilogue, expert_fastest, splits, rows_per_split."""
+    lib = _lib.load()
+    dims = _lib.Dims(B, T, E, K, C, N)
+    info = _lib.PlanInfo()
+    prec, _ = _enums(precision, None)
+    rc = lib.egs_describe_plan({"G": 0, "S": 1, "D": 2}[op], ctypes.byref(dims), _lib.W_CN if w_layout == "cn" else _lib.W_NC,
+                               dtype_to_type_id(dtype), prec, ctypes.byref(info))
+    _lib.check(rc, "egs_describe_plan")
+    return {n: int(getattr(info, n)) for n, _ in _lib.PlanInfo._fields_}
+
+
+_TORCH_INDEX = {torch.int64: _lib.I64, torch.int32: _lib.I32, torch.int16: _lib.I16}
+
+
+def route_topk(scores: torch.Tensor, K: int, *, index_dtype: torch.dtype = torch.int64) -> torch.Tensor:
+    """Expert-choice routing on the device: ``scores`` [B,T,E] -> ``Ind`` [B,E,K], for every (b, e) the K tokens with the
+    highest score, best first (equal scores: lower token id first).  K <= min(T, 1024).  The producer of the ``Ind`` the
+    gather and scatter modules take; the reference has none (its tests draw Ind at random, ``test_all.py:16``)."""
+    lib = _lib.load()
+    if scores.dim() != 3:
+        raise ValueError("expected scores[B,T,E]")
+    dev = _require_cuda(scores)
+    if index_dtype not in _TORCH_INDEX:
+        raise ValueError("index_dtype must be int64, int32 or int16")
+    B, T, E = scores.shape
+    sc = scores.float().contiguous()
+    with torch.cuda.device(dev):
+        Ind = torch.empty((B, E, int(K)), device=dev, dtype=index_dtype)
+        rc = lib.egs_route_topk(sc.data_ptr(), Ind.data_ptr(), B, T, E, int(K), _TORCH_INDEX[index_dtype], _stream_ptr(dev))
+    _lib.check(rc, "egs_route_topk")
+    return Ind
+
+
+class IndexCSR:
+    """Token-major view of an ``Ind`` [B,E,K] built on the device by :func:`build_index_csr`: ``counts`` [B*T] slots per
+    token row, ``offsets`` [B*T+1], ``entries`` [B*E*K] slot ids grouped by token row (ascending inside a row), ``info``
+    [4] = (heaviest row, rows touched, out-of-range flag, valid slots); all int32 CUDA tensors."""
+
+    def __init__(self, counts, offsets, entries, info, B, T, E, K):
+        self.counts, self.offsets, self.entries, self.info = counts, offsets, entries, info
+        self.B, self.T, self.E, self.K = B, T, E, K
+
+    def summary(self) -> dict:
+        """Reads ``info`` back (synchronises)."""
+        v = self.info.tolist()
+        return {"max_per_row": v[0], "rows_touched": v[1], "out_of_range": bool(v[2]), "valid_slots": v[3]}
+
+
+def build_index_csr(Ind: torch.Tensor, T: int) -> IndexCSR:
+    """Counting sort of the routed slots by token row (see :class:`IndexCSR`).  Build it once per step: it serves both
+    scatters of the step (``gemm_scatter(..., csr=...)`` skips its own counting pass) and :func:`gemm_scatter_csr`."""
+    lib = _lib.load()
+    if Ind.dim() != 3:
+        raise ValueError("expected Ind[B,E,K]")
+    dev = _require_cuda(Ind)
+    B, E, K = Ind.shape
+    T = int(T)
+    Ic, it = _index_tensor(Ind)
+    with torch.cuda.device(dev):
+        counts = torch.empty(B * T, device=dev, dtype=torch.int32)
+        offsets = torch.empty(B * T + 1, device=dev, dtype=torch.int32)
+        entries = torch.empty(B * E * K, device=dev, dtype=torch.int32)
+        info = torch.empty(4, device=dev, dtype=torch.int32)
+        sb = int(lib.egs_index_csr_scratch_bytes(B, T))
+        scratch = torch.empty((sb + 3) // 4, device=dev, dtype=torch.int32)
+        rc = lib.egs_index_csr(Ic.data_ptr(), it, B, T, E, K, counts.data_ptr(), offsets.data_ptr(), entries.data_ptr(),
+                               info.data_ptr(), scratch.data_ptr(), sb, _stream_ptr(dev))
+    _lib.check(rc, "egs_index_csr")
+    return IndexCSR(counts, offsets, entries, info, B, T, E, K)
+
+
+def compact_index(Ind: torch.Tensor, T: int, dtype: torch.dtype) -> torch.Tensor:
+    """``Ind`` in a narrower (or wider) integer type, converted on the device; ids outside [0,T) are reported through the
+    status word.  T must fit the target type (int16: T <= 32767)."""
+    lib = _lib.load()
+    dev = _require_cuda(Ind)
+    if dtype not in _TORCH_INDEX:
+        raise ValueError("dtype must be int64, int32 or int16")
+    Ic, it = _index_tensor(Ind)
+    with torch.cuda.device(dev):
+        out = torch.empty(Ic.shape, device=dev, dtype=dtype)
+        rc = lib.egs_index_compact(Ic.data_ptr(), it, Ic.numel(), int(T), out.data_ptr(), _TORCH_INDEX[dtype],
+                                   _status_word(dev).data_ptr(), _stream_ptr(dev))
+    _lib.check(rc, "egs_index_compact")
+    return out
+
+
+def gemm_scatter_csr(Y, W, csr: IndexCSR, *, w_layout="cn", out=None, bias=None):
+    """Operator S evaluated token-major from a CSR: every token row is summed in a fixed order by one CTA and stored (zeros
+    where nothing is routed): no atomics, no zero fill, the same bits on every run.  ``out`` given: added to.  Slower than
+    :func:`gemm_scatter` except for small contractions (it re-reads W[e] per contribution); N <= 1024."""
+    lib = _lib.load()
+    if Y.dim() != 4 or W.dim() != 3:
+        raise ValueError("expected Y[B,E,K,C], W[E,.,.]")
+    dev = _require_cuda(Y, W, csr.entries)
+    if W.dtype != Y.dtype:
+        raise ValueError("Y and W must have the same dtype")
+    dt = dtype_to_type_id(Y.dtype)
+    E, C, N, wl = _w_dims(W, w_layout)
+    B, Ey, K, Cy = Y.shape
+    if (B, Ey, K) != (csr.B, csr.E, csr.K) or Cy != C or Ey != E:
+        raise ValueError("Y, W and the CSR do not describe the same problem")
+    Yc, Wc = Y.contiguous(), W.contiguous()
+    with torch.cuda.device(dev):
+        acc = 0
+        if out is None:
+            out = torch.empty((B, csr.T, N), device=dev, dtype=Y.dtype)
+        else:
+            if tuple(out.shape) != (B, csr.T, N) or out.dtype != Y.dtype or not out.is_contiguous():
+                raise ValueError("out must be a contiguous [B,T,N] tensor of Y's dtype")
+            acc = 1
+        bias_c = _bias_rows(bias, E, N, Y.dtype, dev)
+        dims = _lib.Dims(B, csr.T, E, K, C, N)
+        rc = lib.egs_gemm_scatter_csr(Yc.data_ptr(), Wc.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                      csr.offsets.data_ptr(), csr.entries.data_ptr(), out.data_ptr(), ctypes.byref(dims), wl,
+                                      acc, dt, _stream_ptr(dev))
+    _lib.check(rc, "egs_gemm_scatter_csr")
     return out
 
 

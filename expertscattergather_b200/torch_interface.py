@@ -14,7 +14,8 @@ import math
 import torch
 from torch import nn
 
-from .kernels import ExpertGatherFunction, ExpertGatherScatterFunction, ExpertScatterFunction, create_kernels
+from .kernels import (ExpertGatherBiasFunction, ExpertGatherFunction, ExpertGatherScatterFunction, ExpertScatterBiasFunction,
+                      ExpertScatterFunction, create_kernels)
 
 __all__ = ["ExpertGather", "ExpertScatter", "ExpertGatherScatter"]
 
@@ -43,10 +44,10 @@ class ExpertGather(nn.Module):
             nn.init.uniform_(self.bias, -bound, bound)
 
     def forward(self, x: torch.Tensor, Ind: torch.Tensor) -> torch.Tensor:
-        y = ExpertGatherFunction.apply(x, self.W, Ind)
         if self.bias is not None:
-            y = y + self.bias
-        return y
+            # y + bias ([E,1,J] broadcast over batch and slot, the reference's expression at :55-56), fused into the kernel
+            return ExpertGatherBiasFunction.apply(x, self.W, self.bias, Ind)
+        return ExpertGatherFunction.apply(x, self.W, Ind)
 
 
 class ExpertScatter(nn.Module):
@@ -54,10 +55,19 @@ class ExpertScatter(nn.Module):
 
     ``forward(Y [B,E,K,J], Ind [B,E,K], T) -> [B,T,I]``   (reference: ``egs/torch_interface.py:66-113``)
     The initialisation bound uses ``1/sqrt(I)`` like the reference does (``:93``), although J is the fan-in.
+
+    Bias ([E,1,I], the reference's parameter shape).  The reference adds it to the scattered output with ``out + self.bias``
+    (``:111``), an expression that only broadcasts against ``[B,T,I]`` when E is 1 or B and then pairs expert e with batch
+    element e.  ``bias_mode="per_slot"`` (default) gives the parameter a meaning for every shape: each routed slot of
+    expert e contributes ``Y[b,e,k,:] @ W[e] + bias[e]`` to its token row (fused into the scatter kernel).
+    ``bias_mode="reference"`` evaluates the reference's expression as it stands (and raises where it cannot broadcast).
     """
 
-    def __init__(self, E: int, J: int, I: int, bias: bool = False):
+    def __init__(self, E: int, J: int, I: int, bias: bool = False, bias_mode: str = "per_slot"):
         super().__init__()
+        if bias_mode not in ("per_slot", "reference"):
+            raise ValueError("bias_mode must be 'per_slot' or 'reference'")
+        self.bias_mode = bias_mode
         self.E, self.J, self.I = E, J, I
         self.W = nn.Parameter(torch.empty(E, J, I))
         if bias:
@@ -74,9 +84,11 @@ class ExpertScatter(nn.Module):
             nn.init.uniform_(self.bias, -bound, bound)
 
     def forward(self, Y: torch.Tensor, Ind: torch.Tensor, T: int) -> torch.Tensor:
+        if self.bias is not None and self.bias_mode == "per_slot":
+            return ExpertScatterBiasFunction.apply(Y, self.W, self.bias, Ind, T)
         out = ExpertScatterFunction.apply(Y, self.W, Ind, T)
         if self.bias is not None:
-            out = out + self.bias   # broadcasts like the reference's expression: needs E == B or E == 1
+            out = out + self.bias   # the reference's expression: broadcasts only when E == B or E == 1
         return out
 
 

@@ -99,6 +99,26 @@ int egs_gemm_scatter(const void* Y, const void* W, const void* Ind, void* Out, c
                      int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path,
                      void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
 
+/*
+ * G and S with a per-expert bias fused into the epilogue: bias is [E, N] in the tensors' dtype (NULL = none).
+ *   egs_gather_gemm_bias : Y[b,e,k,:] = X[b, Ind[b,e,k], :] x W(e) + bias[e]     - the `y + self.bias` of the reference's
+ *                          ExpertGather.forward with its [E,1,J] parameter (egs/torch_interface.py:16-19,55), which the
+ *                          reference computes with a separate elementwise kernel.
+ *   egs_gemm_scatter_bias: every routed slot contributes  Y[b,e,k,:] x W(e) + bias[e]  to its token row, i.e.
+ *                          Out[b,t,:] = sum over slots routed to t of (product + bias[e]).  The reference's expression
+ *                          (`out + self.bias` with bias [E,1,I] against out [B,T,I], egs/torch_interface.py:71-74,111)
+ *                          only broadcasts when E is 1 or B and then adds expert e's bias to batch element e; the
+ *                          per-slot form is what a per-expert output bias means for routed tokens and is defined for
+ *                          every shape.
+ * All other arguments as in egs_gather_gemm / egs_gemm_scatter.
+ */
+int egs_gather_gemm_bias(const void* X, const void* W, const void* bias, const void* Ind, void* Y, const egs_dims* dims,
+                         int w_layout, int dtype, int index_dtype, int precision, int path,
+                         int32_t* status_word, void* cuda_stream);
+int egs_gemm_scatter_bias(const void* Y, const void* W, const void* bias, const void* Ind, void* Out, const egs_dims* dims,
+                          int w_layout, int zero_output, int dtype, int index_dtype, int precision, int path,
+                          void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
+
 /* Scratch bytes egs_gemm_scatter needs (0 for float32 tensors; counters + B*T*N*4 for 16-bit ones).  No reference
  * counterpart: the reference adds atomically in the output dtype (egs/triton_kernels.py:247). */
 size_t egs_scatter_workspace_bytes(int64_t B, int64_t T, int64_t N, int dtype);
@@ -179,6 +199,45 @@ int egs_gather_scatter_pair(const void* Src, const void* W1, const void* W2, con
  * 16-bit:  N1 a multiple of 16 and <= 256, C1 and N2 multiples of 8. */
 int egs_fused_pair_eligible(int64_t C1, int64_t N1, int64_t N2, int w_layout, int dtype, int precision);
 
+/*
+ * Router-side index preparation.  The reference has no counterpart: its tests draw Ind with torch.randint (test_all.py:16) and
+ * its scatter resolves collisions with atomics in the output dtype (egs/triton_kernels.py:235-247).
+ *
+ * egs_route_topk: expert-choice routing.  scores [B, T, E] float32 -> Ind [B, E, K] (any index width): for every (b, e) the K
+ *   tokens with the highest score[b, :, e], best first; equal scores go to the lower token id.  K <= min(T, 1024).
+ *
+ * egs_index_csr: token-major CSR of Ind by counting sort (device arrays of int32, caller-owned):
+ *     counts  [B*T]      slots routed to token row b*T + t
+ *     offsets [B*T + 1]  exclusive prefix sums of counts
+ *     entries [B*E*K]    slot ids (b*E + e)*K + k grouped by token row, ascending inside a row (reproducible)
+ *     info    [4]        {heaviest row, token rows touched, 1 if an id lay outside [0,T) (such slots are left out), valid slots}
+ *   scratch: egs_index_csr_scratch_bytes(B, T) bytes.  One build per step serves both scatters of the step.
+ *
+ * egs_index_compact: Ind (any width) -> out_dtype (EGS_I64 / EGS_I32 / EGS_I16), n = B*E*K elements; ids outside [0,T) set
+ *   EGS_STATUS_INDEX_OUT_OF_RANGE in *status_word (may be NULL); T must fit the target width.
+ *
+ * egs_gemm_scatter_prepared: egs_gemm_scatter_bias for a caller that holds the `info` array of egs_index_csr for this Ind: the
+ *   16-bit scatter's choice between direct additions and float32 rows is taken from info[0] instead of a counting pass over
+ *   Ind.  csr_info = NULL makes it egs_gemm_scatter_bias.
+ *
+ * egs_gemm_scatter_csr: operator S evaluated token-major from the CSR: one CTA owns one token row, sums that row's
+ *   contributions in CSR order in float32 and STORES the row (zeros for rows nothing is routed to; accumulate != 0 adds to
+ *   what Out holds instead).  No atomics, no zero fill, no scratch, bit-reproducible.  It re-reads W[e] for every
+ *   contribution, so it is the choice for small contractions or when run-to-run identical bits are required; the
+ *   expert-major kernels behind egs_gemm_scatter are the fast path.  N <= 1024.
+ */
+int egs_route_topk(const float* scores, void* Ind, int64_t B, int64_t T, int64_t E, int64_t K, int index_dtype, void* cuda_stream);
+size_t egs_index_csr_scratch_bytes(int64_t B, int64_t T);
+int egs_index_csr(const void* Ind, int index_dtype, int64_t B, int64_t T, int64_t E, int64_t K, int32_t* counts, int32_t* offsets,
+                  int32_t* entries, int32_t* info, void* scratch, size_t scratch_bytes, void* cuda_stream);
+int egs_index_compact(const void* Ind, int index_dtype, int64_t n, int64_t T, void* out, int out_dtype, int32_t* status_word,
+                      void* cuda_stream);
+int egs_gemm_scatter_prepared(const void* Y, const void* W, const void* bias, const void* Ind, const int* csr_info, void* Out,
+                              const egs_dims* dims, int w_layout, int zero_output, int dtype, int index_dtype, int precision,
+                              int path, void* workspace, size_t workspace_bytes, int32_t* status_word, void* cuda_stream);
+int egs_gemm_scatter_csr(const void* Y, const void* W, const void* bias, const int32_t* offsets, const int32_t* entries, void* Out,
+                         const egs_dims* dims, int w_layout, int accumulate, int dtype, void* cuda_stream);
+
 /* Self-test of the kernels' bounded waits (no reference counterpart).  Launches one CTA that waits, with a limit of
  * limit_cycles SM clocks (at most 2^31, about a second), on a barrier nobody completes.  The wait gives up, the kernel
  * returns normally, EGS_STATUS_PIPELINE_TIMEOUT is set in *status_word, and out2 (two ints on the device) receives
@@ -190,6 +249,23 @@ int egs_selftest_wait_timeout(int32_t* status_word, int* out2, int64_t limit_cyc
  * op: 0 = G, 1 = S, 2 = D (for D pass C=FG, N=FD).  No reference counterpart (diagnostic). */
 int egs_tensor_path_eligible(int op, const egs_dims* dims, int dtype, const void* const* pointers,
                              int n_pointers);
+
+/* Which kernel variant EGS_PATH_AUTO runs for an operator at these sizes on the current device (no launch; base pointers are
+ * assumed 16-byte aligned).  op: 0 = G, 1 = S, 2 = D (for D pass C = FG, N = FD; w_layout is ignored).  Tests use it to make
+ * sure that a case reaches the variant it is meant to cover.  No reference counterpart (the reference autotunes at run time,
+ * egs/triton_kernels.py:38-47). */
+typedef struct egs_plan_info {
+  int tensor_path;    /* 1: tcgen05 tensor-core kernels, 0: generic CUDA-core kernels (the fields below are then 0) */
+  int tile_n;         /* tile width over the produced features */
+  int stages;         /* depth of the shared-memory stage ring */
+  int row_tiles;      /* 128-row accumulator tiles per CTA: 1 or 2 */
+  int persistent;     /* G / S: 1 = the persistent warp-specialised kernel */
+  int bulk_epilogue;  /* S with 16-bit tensors: direct additions go out as bulk reductions */
+  int expert_fastest; /* G / S: grid order, 1 = experts vary fastest */
+  int splits;         /* D: row ranges the contraction is split into */
+  int rows_per_split; /* D: contraction rows per range */
+} egs_plan_info;
+int egs_describe_plan(int op, const egs_dims* dims, int w_layout, int dtype, int precision, egs_plan_info* out);
 
 /* Zero-fills n bytes at p on the stream with the library's own fill kernel (what zero_output uses).
  * Replaces the torch.zeros_like calls of the reference's wrappers (egs/triton_kernels.py:408-409). */

@@ -9,7 +9,8 @@ import expertscattergather_b200 as egs
 from conftest import golden_names, load_golden
 from expertscattergather_b200 import ops, workloads
 from expertscattergather_b200.workloads import Workload
-from gpu_util import STEP_KEYS, compare_step, eligible, gpu_step, to_dev, tol_for
+from expertscattergather_b200.step import train_step
+from gpu_util import STEP_KEYS, TOL, compare_step, eligible, gpu_step, to_dev, tol_for
 from oracle import egs_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -407,3 +408,97 @@ def test_weight_gradient_into_a_prezeroed_output(cuda_device):
     assert got is buf and torch.equal(got, plain)
     with pytest.raises(ValueError, match="float32"):
         ops.dweight(d["X"].bfloat16(), Y.bfloat16(), d["Ind"], zeroed_out=buf)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# full benchmark sizes of the tensor-bound configurations: all six outputs, element by element
+# ---------------------------------------------------------------------------------------------------------
+def _checker_step_on_device(d, chunk):
+    """The oracle's torch restatement (oracle.torch_step: gather + einsum + scatter_add_, gradients by autograd) evaluated
+    on the GPU in float32 over batch chunks, the weight gradients summed over the chunks in float32.  For these two
+    cases only this stands in for the CPU run of the same functions, which needs minutes at these sizes; the inputs are
+    the test's 16-bit tensors upcast, so it differs from exact arithmetic by float32 rounding only."""
+    X, Wg, Ws, Ind, G = (d[k] for k in ("X", "Wg", "Ws", "Ind", "G"))
+    Wg32, Ws32 = Wg.float(), Ws.float()
+    outs = {k: [] for k in ("Y", "Out", "dY", "dX")}
+    dWg = torch.zeros_like(Wg32)
+    dWs = torch.zeros_like(Ws32)
+    for b0 in range(0, X.shape[0], chunk):
+        sl = slice(b0, b0 + chunk)
+        r = orc.torch_step(X[sl].float(), Wg32, Ws32, Ind[sl], G[sl].float())
+        for k in outs:
+            outs[k].append(r[k])
+        dWg += r["dWg"]
+        dWs += r["dWs"]
+    res = {k: torch.cat(v) for k, v in outs.items()}
+    res["dWg"], res["dWs"] = dWg, dWs
+    return res
+
+
+def _rel_err_on_device(a, ref):
+    return float((a.float() - ref).abs().max() / ref.abs().max())
+
+
+@pytest.mark.parametrize("name,B,chunk", [("cfg4", 64, 8), ("cfg3", 8, 2)])
+def test_full_size_parity_of_the_tensor_bound_configurations(cuda_device, name, B, chunk):
+    """cfg4 at its per-GPU batch (64) and cfg3 at full size through the explicit step: every element of Y, Out, dY, dX, dW_g
+    and dW_s against the checker, and the kernel variants the benchmark times at these sizes must be the ones that ran
+    (256-row gather CTAs, the persistent scatter with bulk reductions, two-accumulator weight-gradient CTAs)."""
+    w = workloads.WORKLOADS[name].with_batch(B)
+    plan_g = ops.describe_plan("G", B, w.T, w.E, w.K, w.I, w.J, w.dtype)
+    plan_s = ops.describe_plan("S", B, w.T, w.E, w.K, w.J, w.I, w.dtype)
+    plan_d = ops.describe_plan("D", B, w.T, w.E, w.K, w.I, w.J, w.dtype)
+    assert plan_g["tensor_path"] and plan_g["row_tiles"] == 2, plan_g
+    assert plan_d["tensor_path"] and plan_d["row_tiles"] == 2, plan_d
+    if name == "cfg4":
+        assert plan_s["persistent"] == 1 and plan_s["bulk_epilogue"] == 1 and plan_s["expert_fastest"] == 1, plan_s
+    else:
+        assert plan_s["tensor_path"] == 1 and plan_s["persistent"] == 0, plan_s
+    d = to_dev(workloads.make_inputs(w), cuda_device)
+    ops.reset_status()
+    got = train_step(d["X"], d["Wg"], d["Ws"], d["Ind"], d["G"])
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = _checker_step_on_device(d, chunk)
+    errs = {k: _rel_err_on_device(got[k], ref[k]) for k in ("Y", "Out", "dY", "dX", "dWg", "dWs")}
+    assert all(e <= TOL["bf16"] for e in errs.values()), errs
+    # the fused 16-bit pair kernel at the same size (cfg4: middle width 256 fits; cfg3's 512 does not)
+    if ops.fused_pair_eligible(w.I, w.J, w.I, w.dtype):
+        Y, Out = ops.gather_scatter_pair(d["X"], d["Wg"], d["Ws"], d["Ind"])
+        dY, dX = ops.gather_scatter_pair(d["G"], d["Ws"], d["Wg"], d["Ind"], w_layout="nc")
+        torch.cuda.synchronize()
+        ops.check_status()
+        perr = {"Y": _rel_err_on_device(Y, ref["Y"]), "Out": _rel_err_on_device(Out, ref["Out"]),
+                "dY": _rel_err_on_device(dY, ref["dY"]), "dX": _rel_err_on_device(dX, ref["dX"])}
+        assert all(e <= TOL["bf16"] for e in perr.values()), perr
+
+
+def test_strict_float32_on_long_contractions(cuda_device):
+    """Strict float32 is three TF32 products per element (hi*hi + hi*lo + lo*hi) summed in the tensor core's float32
+    accumulator, whose additions truncate: the error grows with the number of accumulation steps (3.3e-5 at a contraction
+    of 4096, 1.5e-5 after 8192 rows of D were measured with everything on the tensor cores).  The library therefore
+    bounds what one accumulator sees: G / S beyond a contraction of 512 take the FFMA kernels, D splits its rows into
+    ranges of at most 1024 whose partial tiles are summed by float32 atomics.  Checked against float64 truth."""
+    w = Workload("long", 64, 512, 2, 128, 4096, 64, torch.float32, "distinct", 99)
+    ins = workloads.make_inputs(w)
+    d = to_dev(ins, cuda_device)
+    assert ops.describe_plan("G", w.B, w.T, w.E, w.K, w.I, w.J, w.dtype, precision="strict")["tensor_path"] == 0
+    plan_d = ops.describe_plan("D", w.B, w.T, w.E, w.K, w.I, w.J, w.dtype, precision="strict")
+    assert plan_d["tensor_path"] == 1 and plan_d["rows_per_split"] <= 1024, plan_d
+    ops.reset_status()
+    Y = ops.gather_gemm(d["X"], d["Wg"], d["Ind"], precision="strict")
+    dWg = ops.dweight(d["X"], Y, d["Ind"], precision="strict")
+    torch.cuda.synchronize()
+    ops.check_status()
+    e_g = orc.rel_err(Y.cpu(), orc.np_gather(ins["X"], ins["Wg"], ins["Ind"]))
+    e_d = orc.rel_err(dWg.cpu(), orc.np_dweight(ins["X"], Y.cpu(), ins["Ind"]))
+    # the longest contraction that stays on the tensor cores in strict mode
+    w2 = Workload("long512", 16, 256, 4, 64, 512, 64, torch.float32, "distinct", 98)
+    ins2 = workloads.make_inputs(w2)
+    d2 = to_dev(ins2, cuda_device)
+    assert ops.describe_plan("G", w2.B, w2.T, w2.E, w2.K, w2.I, w2.J, w2.dtype, precision="strict")["tensor_path"] == 1
+    Y2 = ops.gather_gemm(d2["X"], d2["Wg"], d2["Ind"], precision="strict")
+    torch.cuda.synchronize()
+    e_g2 = orc.rel_err(Y2.cpu(), orc.np_gather(ins2["X"], ins2["Wg"], ins2["Ind"]))
+    print(f"strict float32: G C=4096 (FFMA) {e_g:.2e}, G C=512 (tensor cores) {e_g2:.2e}, D 8192 rows in ranges of <=1024 {e_d:.2e}")
+    assert e_g <= TOL["fp32"] and e_g2 <= TOL["fp32"] and e_d <= TOL["fp32"], (e_g, e_g2, e_d)
