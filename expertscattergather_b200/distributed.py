@@ -14,7 +14,7 @@ from typing import Iterable, Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["init_from_env", "shard_bounds", "shard_batch", "GradAllReducer", "dp_train_step"]
+__all__ = ["init_from_env", "shard_bounds", "shard_batch", "GradAllReducer", "dp_train_step", "t_sharded_scatter"]
 
 
 def init_from_env(backend: Optional[str] = None) -> tuple[int, int, int]:
@@ -95,3 +95,36 @@ def dp_train_step(X, Wg, Ws, Ind, G, group=None, step_fn=None) -> dict:
     out = step_fn(X, Wg, Ws, Ind, G, on_weight_grad=lambda _name, t: reducer.reduce_async(t))
     reducer.finish()
     return out
+
+
+
+def t_sharded_scatter(Y, W, Ind, T: int, group=None, scatter_fn=None) -> torch.Tensor:
+    """Scatter with the experts sharded over the ranks and the OUTPUT sharded over the sequence: for sequences so long
+    that no rank should hold (or add into) the whole ``[B,T,I]`` result.
+
+    Every rank passes the slices of its own experts - ``Y`` [B,E_r,K,J], ``W`` [E_r,J,I], ``Ind`` [B,E_r,K] - computes
+    their contribution to all token rows with the scatter operator and the ranks' contributions are summed with a
+    reduce-scatter over the token axis: rank r returns ``Out[:, lo_r:hi_r, :]`` for its contiguous token range
+    (``shard_bounds(T, r, world)``).  T must be divisible by the world size for the NCCL reduce-scatter; otherwise (and
+    with backends that have no reduce-scatter, such as gloo) the sum is an all-reduce followed by a slice.
+    ``scatter_fn(Y, W, Ind, T) -> [B,T,I]`` defaults to the CUDA operator; the CPU tests pass a checker instead.
+    No counterpart in the reference, which is single-GPU.
+    """
+    if scatter_fn is None:
+        from . import ops
+
+        def scatter_fn(y, w, ind, t):
+            return ops.gemm_scatter(y, w, ind, t, w_layout="cn")
+    partial = scatter_fn(Y, W, Ind, T)
+    if not (dist.is_initialized() and dist.get_world_size(group) > 1):
+        return partial
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    lo, hi = shard_bounds(T, rank, world)
+    if dist.get_backend(group) == "nccl" and T % world == 0:
+        # reduce_scatter_tensor splits its input along dim 0: put the token axis first
+        tb = partial.transpose(0, 1).contiguous()                     # [T, B, I]
+        out = torch.empty((T // world,) + tuple(tb.shape[1:]), device=tb.device, dtype=tb.dtype)
+        dist.reduce_scatter_tensor(out, tb, op=dist.ReduceOp.SUM, group=group)
+        return out.transpose(0, 1).contiguous()
+    dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
+    return partial[:, lo:hi, :].contiguous()

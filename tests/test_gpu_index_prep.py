@@ -106,12 +106,16 @@ def test_scatter_takes_its_plan_from_a_prepared_csr(cuda_device):
     """The 16-bit scatter with csr=... must equal the one that counts for itself, in both regimes (few contributions per
     row: direct 16-bit additions; a Zipf index: float32 rows)."""
     for index in ("distinct", "zipf"):
-        w = Workload("prep", 4, 128, 32, 32, 64, 128, torch.bfloat16, index, 71)
+        w = Workload("prep", 4, 256, 48, 32, 64, 128, torch.bfloat16, index, 71)
         d = to_dev(workloads.make_inputs(w), cuda_device)
         Y = ops.gather_gemm(d["X"], d["Wg"], d["Ind"])
         csr = ops.build_index_csr(d["Ind"], w.T)
         a = ops.gemm_scatter(Y, d["Ws"], d["Ind"], w.T)
         b = ops.gemm_scatter(Y, d["Ws"], d["Ind"], w.T, csr=csr)
-        assert orc.rel_err(b.cpu(), a.cpu()) <= 1e-2
-        heavy = csr.summary()["max_per_row"] > 32
-        assert heavy == (index == "zipf")
+        ref = orc.np_scatter(Y.cpu(), d["Ws"].cpu(), d["Ind"].cpu(), w.T)
+        # (direct 16-bit additions round in the order they happen to run in: both against the float64 truth)
+        assert orc.rel_err(a.cpu(), ref) <= 3e-2 and orc.rel_err(b.cpu(), ref) <= 3e-2
+        flat = (d["Ind"].cpu() + torch.arange(w.B).view(-1, 1, 1) * w.T).reshape(-1)
+        heaviest = int(torch.bincount(flat).max())
+        assert csr.summary()["max_per_row"] == heaviest
+        assert (heaviest > 32) == (index == "zipf"), heaviest      # the two cases sit on either side of the 32-per-row switch
