@@ -21,7 +21,7 @@ TOL_BF16 = 3e-2     # max|a-b| / max|b|, the bf16 tolerance of the parity tests
 
 
 def _rel(a, b):
-    a, b = a.float(), b.float()
+    a, b = a.detach().cpu().double(), b.detach().cpu().double()
     return float((a - b).abs().max() / b.abs().max())
 
 
