@@ -87,7 +87,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
-// TMA tile load (no multicast): box of a 3-D tensor map -> shared memory of this CTA, bytes counted on `bar`.
+// TMA tile load into this CTA's own shared memory: box of a 3-D tensor map, bytes counted on `bar`.
 // The innermost coordinate times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int x, int y, int z, uint32_t bar) {
   asm volatile(
