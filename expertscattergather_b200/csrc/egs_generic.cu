@@ -225,12 +225,17 @@ __global__ void __launch_bounds__(256) fill_zero_bytes_kernel(unsigned char* p, 
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = 0;
 }
 
+template <typename T> __device__ __forceinline__ void convert8(const float* __restrict__ src, T* __restrict__ dst);
+
 template <typename T>
 __global__ void __launch_bounds__(256) convert_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst,
                                                               size_t n) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    dst[i] = from_f32<T>(src[i]);
+  const size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool vec = sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+  const size_t n8 = vec ? n / 8 : 0;
+  for (size_t i = i0; i < n8; i += stride) convert8<T>(src + 8 * i, dst + 8 * i);
+  for (size_t i = n8 * 8 + i0; i < n; i += stride) dst[i] = from_f32<T>(src[i]);
 }
 
 template <typename T>
@@ -281,13 +286,28 @@ __global__ void __launch_bounds__(256) scatter_init_kernel(const int* __restrict
   }
 }
 
+// 8 float32 values -> 8 elements of T with vector loads and one 16-byte store (T is a 16-bit type)
+template <typename T>
+__device__ __forceinline__ void convert8(const float* __restrict__ src, T* __restrict__ dst) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  T v[8] = {from_f32<T>(a.x), from_f32<T>(a.y), from_f32<T>(a.z), from_f32<T>(a.w),
+            from_f32<T>(b.x), from_f32<T>(b.y), from_f32<T>(b.z), from_f32<T>(b.w)};
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) scatter_finish_kernel(const int* __restrict__ plan, const float* __restrict__ acc,
                                                             T* __restrict__ out, size_t n) {
   if (!*plan) return;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    out[i] = from_f32<T>(acc[i]);
+  const size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (sizeof(T) == 2) {          // (both buffers are 16-byte aligned: checked on the host)
+    const size_t n8 = n / 8;
+    for (size_t i = i0; i < n8; i += stride) convert8<T>(acc + 8 * i, out + 8 * i);
+    for (size_t i = n8 * 8 + i0; i < n; i += stride) out[i] = from_f32<T>(acc[i]);
+  } else {
+    for (size_t i = i0; i < n; i += stride) out[i] = from_f32<T>(acc[i]);
+  }
 }
 
 int grid_for(size_t work_items, int per_block) {
