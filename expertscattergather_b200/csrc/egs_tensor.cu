@@ -707,12 +707,36 @@ __global__ void __launch_bounds__(PersistShape<SCATTER>::kThreads, 1) tensor_row
       const RowBlock blk = row_block_of(p, rb, m_tiles);
       const char* a_src[kTileM / RS];
       uint32_t a_mask = 0;
+      int src_rows[kTileM / RS];
+      if (SCATTER) {
+        // the source rows of S are the slot rows themselves: no index is read here (a slot whose index is out of range
+        // is dropped by the epilogue, which has no destination row for it)
+#pragma unroll
+        for (int i = 0; i < kTileM / RS; ++i) {
+          const int m = blk.m0 + r0 + RS * i;
+          const int b = m / p.K, k = m - b * p.K;
+          src_rows[i] = (m < p.M) ? (b * p.E + blk.e) * p.K + k : -1;
+        }
+      } else {
+        // all index loads are issued before the first one is looked at
+        long long tk[kTileM / RS];
+        int brow[kTileM / RS];
+#pragma unroll
+        for (int i = 0; i < kTileM / RS; ++i) {
+          const int m = blk.m0 + r0 + RS * i;
+          const bool on = m < p.M;
+          const int b = on ? m / p.K : 0, k = on ? m - b * p.K : 0;
+          brow[i] = on ? b * p.T : -1;
+          tk[i] = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + blk.e) * p.K + k);
+        }
+#pragma unroll
+        for (int i = 0; i < kTileM / RS; ++i)
+          src_rows[i] = (brow[i] >= 0 && tk[i] >= 0 && tk[i] < p.T) ? brow[i] + static_cast<int>(tk[i]) : -1;
+      }
 #pragma unroll
       for (int i = 0; i < kTileM / RS; ++i) {
-        int src_row, dst_row;
-        lookup_rows<SCATTER>(p, blk.e, blk.m0 + r0 + RS * i, src_row, dst_row, false);
-        a_src[i] = A + (src_row >= 0 ? static_cast<long long>(src_row) * row_bytes_a : 0ll) + cc * 16;
-        if (src_row >= 0) a_mask |= 1u << i;
+        a_src[i] = A + (src_rows[i] >= 0 ? static_cast<long long>(src_rows[i]) * row_bytes_a : 0ll) + cc * 16;
+        if (src_rows[i] >= 0) a_mask |= 1u << i;
       }
       const bool a_full = (a_mask == (1u << (kTileM / RS)) - 1u);
       for (int nt = 0; nt < n_tiles && alive; ++nt) {
@@ -967,14 +991,29 @@ __global__ void __launch_bounds__(kThreads, MT == 2 ? 1 : 2) tensor_dweight_kern
   pp.nk = (rows + KR - 1) / KR;
 
   // ---- set-up: token-row table (coalesced reads of Ind), barriers, tensor memory ----
-  for (int i = tid; i < rows; i += kThreads) {
-    const int m = m_begin + i;
-    const int b = m / p.K, k = m - b * p.K;
-    const long long t = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + e) * p.K + k);
-    int tok = -1;
-    if (t >= 0 && t < p.T) tok = b * p.T + static_cast<int>(t);
-    else if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
-    row_tok[i] = tok;
+  // (eight index loads are in flight per thread before the first is looked at: one load per round trip would make
+  // this table the longest part of the set-up)
+  for (int i0 = tid; i0 < rows; i0 += 8 * kThreads) {
+    long long tk[8];
+    int brow[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kThreads;
+      const bool on = i < rows;
+      const int m = m_begin + (on ? i : 0);
+      const int b = m / p.K, k = m - b * p.K;
+      brow[j] = on ? b * p.T : -1;
+      tk[j] = load_index(p.Ind, p.index_dtype, static_cast<long long>(b * p.E + e) * p.K + k);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (brow[j] >= 0) {
+        int tok = -1;
+        if (tk[j] >= 0 && tk[j] < p.T) tok = brow[j] + static_cast<int>(tk[j]);
+        else if (p.status) atomicOr(p.status, EGS_STATUS_INDEX_OUT_OF_RANGE);
+        row_tok[i0 + j * kThreads] = tok;
+      }
+    }
   }
   const uint32_t acc_cols = tmem_cols_for(p.BN);
   const uint32_t tmem_cols = acc_cols * MT;
