@@ -32,7 +32,7 @@ constexpr long long kWaitLimitCycles = 1LL << 31;   // about a second at B200 cl
 // taking issue slots away from the warps that have work.
 constexpr uint32_t kTryWaitSuspendNs = 1000000u;
 
-constexpr int kMaxRowsPerSplit = 4096;   // operator D: contraction rows one CTA may own (row table in smem)
+constexpr int kMaxRowsPerSplit = 8192;   // operator D: contraction rows one CTA may own (row table in smem, 32 KB)
 
 struct __align__(16) SmemHeader {
   unsigned long long full[kMaxStages];
