@@ -12,6 +12,7 @@ inside the timed step.  At N=1 the line also carries a `configs` array with the 
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -31,6 +32,7 @@ L2_BYTES = 126 * 1024 * 1024
 METRIC = "gather+scatter fwd+bwd routed tokens/s"
 DEFAULT_WORKLOAD = "cfg4"
 ALL_CONFIGS = ("cfg0", "cfg1-sweep", "cfg2", "cfg3", "cfg4")
+E2E_MICRO_BATCH = 64     # batch elements per micro-batch of the end-to-end leg (a pass of at most this size is one copy)
 
 
 def measured_peaks():
@@ -605,30 +607,44 @@ def main():
         h2d = sum(h[k].numel() * h[k].element_size() for h in host for k in ("X", "Ind", "G"))
         d2h = sum(a.numel() * a.element_size() + b.numel() * b.element_size() + 4 for a, b, _ in res_host)
         copy_stream = torch.cuda.Stream(dev)
+        # A pass whose batch is large goes through the modules in micro-batches of E2E_MICRO_BATCH batch elements, the
+        # way a training loop feeds host-resident data: the copy of micro-batch i+1 runs under the kernels of
+        # micro-batch i, the weight gradients accumulate in .grad, and only the accumulated gradient is reduced over the
+        # ranks (GradAllReducer.no_sync) and copied back.
+        def micro_slices(nb):
+            mb = E2E_MICRO_BATCH if (nb > E2E_MICRO_BATCH and nb % E2E_MICRO_BATCH == 0) else nb
+            return [(lo, lo + mb) for lo in range(0, nb, mb)]
+        micro = [micro_slices(h["X"].shape[0]) for h in host]
 
         def e2e_step():
-            # the host->device copies of all passes are queued on a copy stream at the start of the step (pinned
-            # buffers, one event per pass); the compute stream waits for each pass's event, so the copies of the next
-            # pass run under the kernels of the current one, as an input prefetcher of a training loop would do
+            # all host->device copies of the step are queued on a copy stream at its start (pinned buffers, one event per
+            # micro-batch); the compute stream waits for each micro-batch's event
             main_s = torch.cuda.current_stream(dev)
             copy_stream.wait_stream(main_s)
             staged = []
             with torch.cuda.stream(copy_stream):
-                for h in host:
-                    t = tuple(h[k].to(dev, non_blocking=True) for k in ("X", "Ind", "G"))
-                    staged.append((t, copy_stream.record_event()))
-            for w, (t, ready), (g, s), (rg, rs, rl) in zip(passes, staged, mods, res_host):
-                main_s.wait_event(ready)
-                for x in t:
-                    x.record_stream(main_s)
-                X, Ind, G = t[0].requires_grad_(True), t[1], t[2]
+                for h, sl in zip(host, micro):
+                    chunks = []
+                    for lo, hi in sl:
+                        t = tuple(h[k][lo:hi].to(dev, non_blocking=True) for k in ("X", "Ind", "G"))
+                        chunks.append((t, copy_stream.record_event()))
+                    staged.append(chunks)
+            for w, chunks, (g, s), (rg, rs, rl) in zip(passes, staged, mods, res_host):
                 g.W.grad = None; s.W.grad = None
-                Out = s(g(X, Ind), Ind, w.T)
-                loss = (Out * G).sum()
-                loss.backward()
+                loss_sum = None
+                for ci, (t, ready) in enumerate(chunks):
+                    main_s.wait_event(ready)
+                    for x in t:
+                        x.record_stream(main_s)
+                    X, Ind, G = t[0].requires_grad_(True), t[1], t[2]
+                    with (reducer.no_sync() if ci + 1 < len(chunks) else contextlib.nullcontext()):
+                        Out = s(g(X, Ind), Ind, w.T)
+                        loss = (Out * G).sum()
+                        loss.backward()
+                    loss_sum = loss.detach().float() if loss_sum is None else loss_sum + loss.detach().float()
                 reducer.finish()
                 rg.copy_(g.W.grad, non_blocking=True); rs.copy_(s.W.grad, non_blocking=True)
-                rl.copy_(loss.detach().float().reshape(1), non_blocking=True)
+                rl.copy_(loss_sum.reshape(1), non_blocking=True)
             torch.cuda.synchronize()
 
         for _ in range(3):
@@ -645,6 +661,7 @@ def main():
         e2e = {"value": tokens_per_step * n_e2e / float(dt.item()), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "copied_in": "X, Ind, G (pinned host buffers) every step",
+               "micro_batches": [len(sl) for sl in micro],
                "copied_back": "dW_g, dW_s and the loss every step (dX stays on the device)",
                "api": "ExpertGather / ExpertScatter modules + autograd"}
         ops.check_status()

@@ -8,6 +8,7 @@ this module is new functionality built on ``torch.distributed`` (NCCL on GPUs, g
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from typing import Iterable, Optional
 
@@ -52,12 +53,24 @@ class GradAllReducer:
     ``attach(params)`` registers a post-accumulate-grad hook per parameter that starts an asynchronous
     all-reduce of ``param.grad``; ``finish()`` waits for all of them.  With the gather and scatter modules in
     one model the scatter weight's reduction is in flight while the gather backward still computes.
+    Gradient accumulation over micro-batches: run all backward passes but the last inside ``no_sync()`` (the
+    meaning of ``DistributedDataParallel.no_sync``), so that only the accumulated gradient is reduced.
     """
 
     def __init__(self, group=None):
         self.group = group
         self._pending = []
         self._handles = []
+        self._sync = True
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context add to ``.grad`` without starting a reduction."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
 
     def attach(self, params: Iterable[torch.nn.Parameter]) -> "GradAllReducer":
         for p in params:
@@ -66,7 +79,8 @@ class GradAllReducer:
         return self
 
     def _hook(self, param: torch.nn.Parameter) -> None:
-        self.reduce_async(param.grad)
+        if self._sync:
+            self.reduce_async(param.grad)
 
     def reduce_async(self, t: torch.Tensor) -> None:
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:

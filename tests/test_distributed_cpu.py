@@ -1,5 +1,6 @@
 """Batch sharding + weight-gradient all-reduce over gloo (world_size 2), with the CPU checker as the
 per-rank step, compared with the unsharded result."""
+import contextlib
 import os
 import socket
 
@@ -50,7 +51,21 @@ def _worker(rank, world, port, B, result_dir):
     (O * sl["G"]).sum().backward()
     red.finish()
     red.detach()
-    torch.save({"dWg": out["dWg"], "dWs": out["dWs"], "dX": out["dX"], "hook_dWg": Wg.grad, "hook_dWs": Ws.grad},
+    # (c) the same with the slice cut into micro-batches: gradients accumulate locally, one reduction at the end
+    Wg2 = torch.nn.Parameter(full["Wg"].clone())
+    Ws2 = torch.nn.Parameter(full["Ws"].clone())
+    red2 = egd.GradAllReducer().attach([Wg2, Ws2])
+    nb = sl["X"].shape[0]
+    for b in range(nb):
+        ctx = red2.no_sync() if b < nb - 1 else contextlib.nullcontext()
+        with ctx:
+            Yb = orc.torch_gather(sl["X"][b:b + 1], Wg2, sl["Ind"][b:b + 1])
+            Ob = orc.torch_scatter(Yb, Ws2, sl["Ind"][b:b + 1], wl.T)
+            (Ob * sl["G"][b:b + 1]).sum().backward()
+    red2.finish()
+    red2.detach()
+    torch.save({"dWg": out["dWg"], "dWs": out["dWs"], "dX": out["dX"], "hook_dWg": Wg.grad, "hook_dWs": Ws.grad,
+                "micro_dWg": Wg2.grad, "micro_dWs": Ws2.grad},
                os.path.join(result_dir, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -72,6 +87,7 @@ def test_two_rank_sharded_step_matches_unsharded(tmp_path, B):
         for k in ("dWg", "dWs"):
             assert torch.allclose(p[k], ref[k], rtol=1e-12, atol=1e-12), (r, k)
             assert torch.allclose(p["hook_" + k], ref[k], rtol=1e-12, atol=1e-12), (r, "hook", k)
+            assert torch.allclose(p["micro_" + k], ref[k], rtol=1e-12, atol=1e-12), (r, "micro-batches", k)
         lo, hi = shard_bounds(B, r, world)
         assert torch.allclose(p["dX"], ref["dX"][lo:hi], rtol=1e-12, atol=1e-12)
 
