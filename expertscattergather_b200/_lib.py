@@ -15,7 +15,7 @@ from . import build as _build
 F32, F16, BF16 = 0, 1, 2
 I16, I32, I64 = 0, 1, 2
 PREC_STRICT, PREC_TF32 = 0, 1
-PATH_AUTO, PATH_GENERIC, PATH_TENSOR = 0, 1, 2
+PATH_AUTO, PATH_GENERIC, PATH_TENSOR, PATH_PAIRED = 0, 1, 2, 3
 W_CN, W_NC = 0, 1
 DW_GATHERED_ROWS, DW_DIRECT_ROWS = 0, 1
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TOO_LARGE = range(6)

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT_DIR = os.path.join(PKG, "_lib")
 LIB_PATH = os.path.join(OUT_DIR, "libegs_b200.so")
-SOURCES = ["egs_api.cu", "egs_generic.cu", "egs_tensor.cu", "egs_pair16.cu", "egs_index.cu"]
+SOURCES = ["egs_api.cu", "egs_generic.cu", "egs_tensor.cu", "egs_pair16.cu", "egs_gather2.cu", "egs_index.cu"]
 HEADERS = [os.path.join(CSRC, "egs_internal.cuh"), os.path.join(CSRC, "egs_tcgen05.cuh"), os.path.join(PKG, "..", "include", "egs_b200.h")]
 
 

@@ -100,8 +100,9 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* bias, co
   if (int rc = check_dims(dims)) return rc;
   if (!valid_dtype(dtype) || !valid_index(index_dtype) || (w_layout != EGS_W_CN && w_layout != EGS_W_NC) ||
       (precision != EGS_PREC_STRICT && precision != EGS_PREC_TF32) ||
-      (path != EGS_PATH_AUTO && path != EGS_PATH_GENERIC && path != EGS_PATH_TENSOR))
+      (path != EGS_PATH_AUTO && path != EGS_PATH_GENERIC && path != EGS_PATH_TENSOR && path != EGS_PATH_PAIRED))
     return EGS_ERR_INVALID_ARGUMENT;
+  if (path == EGS_PATH_PAIRED && (scatter || dtype == EGS_F32)) return EGS_ERR_UNSUPPORTED;
   const egs_dims& d = *dims;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long out_rows = scatter ? d.B * d.T : d.B * d.E * d.K;
@@ -119,13 +120,14 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* bias, co
   float* acc = nullptr;
   int* plan = nullptr;
   const bool eligible = device_is_sm100() && rowgemm_tensor_ok(d, dtype, A, W, Out);
-  if (path == EGS_PATH_TENSOR && !eligible) return EGS_ERR_UNSUPPORTED;
+  if ((path == EGS_PATH_TENSOR || path == EGS_PATH_PAIRED) && !eligible) return EGS_ERR_UNSUPPORTED;
   // Strict float32 on long contractions: the tensor core's accumulator additions truncate, and the error grows with the
   // contraction length (3.3e-5 of max|ref| at C = 4096 against the 1e-5 bar).  EGS_PATH_AUTO therefore keeps strict
   // float32 on the tensor cores only up to kStrictMaxContraction and takes the FFMA kernels beyond.
   const bool strict_long = (dtype == EGS_F32 && precision == EGS_PREC_STRICT && d.C > kStrictMaxContraction);
-  const bool tensor = ((path == EGS_PATH_TENSOR) || (path == EGS_PATH_AUTO && eligible && !strict_long)) && !(d.C == 0) &&
+  const bool tensor = ((path == EGS_PATH_TENSOR || path == EGS_PATH_PAIRED) || (path == EGS_PATH_AUTO && eligible && !strict_long)) && !(d.C == 0) &&
                       (bias == nullptr || aligned16(bias));
+  if (path == EGS_PATH_PAIRED && !tensor) return EGS_ERR_UNSUPPORTED;
   if (f32_rows) {
     const size_t need = egs_scatter_workspace_bytes(d.B, d.T, d.N, dtype);
     if (!workspace || workspace_bytes < need || !aligned16(workspace)) return EGS_ERR_WORKSPACE;
@@ -178,8 +180,14 @@ int run_rowgemm(bool scatter, const void* A, const void* W, const void* bias, co
   cudaError_t err;
   if (tensor) {
     p.expert_fastest = pick_expert_fastest(d, scatter, dtype);
-    const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
-    err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
+    if (path == EGS_PATH_PAIRED) {
+      const size_t smem2 = configure_tensor_gather2(p);
+      if (smem2 == 0) return EGS_ERR_UNSUPPORTED;
+      err = launch_tensor_gather2(p, dtype, smem2, st);
+    } else {
+      const size_t smem = configure_tensor_rowgemm(p, scatter, dtype, precision);
+      err = launch_tensor_rowgemm(p, scatter, dtype, precision, smem, st);
+    }
   } else {
     err = launch_generic_rowgemm(p, scatter, dtype, st);
   }

@@ -130,6 +130,9 @@ cudaError_t launch_tensor_dweight(const DWeightParams& p, int dtype, int precisi
 size_t configure_tensor_fused_pair(FusedParams& p, int precision);
 cudaError_t launch_tensor_fused_pair(const FusedParams& p, int precision, size_t smem_bytes, cudaStream_t st);
 // Fused pair for 16-bit tensors (persistent kernel, egs_pair16.cu); same conventions.
+// Operator G on pairs of SMs (egs_gather2.cu, EGS_PATH_PAIRED): fills BN / stages, returns the shared memory size or 0.
+size_t configure_tensor_gather2(RowGemmParams& p);
+cudaError_t launch_tensor_gather2(const RowGemmParams& p, int dtype, size_t smem_bytes, cudaStream_t st);
 size_t configure_tensor_pair16(FusedParams& p);
 cudaError_t launch_tensor_pair16(const FusedParams& p, int dtype, size_t smem_bytes, cudaStream_t st);
 

@@ -17,7 +17,8 @@ __all__ = ["gather_gemm", "gemm_scatter", "gather_scatter_pair", "fused_pair_eli
            "check_status", "reset_status", "publish_status", "launch_count", "dtype_to_type_id", "tensor_path_eligible", "describe_plan", "route_topk", "build_index_csr", "compact_index", "gemm_scatter_csr", "IndexCSR"]
 
 _PRECISIONS = {"strict": _lib.PREC_STRICT, "fp32": _lib.PREC_STRICT, "tf32": _lib.PREC_TF32}
-_PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR}
+_PATHS = {"auto": _lib.PATH_AUTO, "generic": _lib.PATH_GENERIC, "tensor": _lib.PATH_TENSOR,
+          "paired": _lib.PATH_PAIRED}     # "paired": per-call only, operator G on 16-bit tensors (see gather_gemm)
 _SM_COUNT = 148     # B200
 
 _state = {
@@ -43,7 +44,7 @@ def get_precision() -> str:
 
 def set_path(path: str) -> None:
     """'auto' (tensor-core kernels when the shape is eligible), 'generic' or 'tensor'."""
-    if path not in _PATHS:
+    if path not in _PATHS or path == "paired":
         raise ValueError(f"unknown path {path!r}")
     _state["path"] = path
 
@@ -236,7 +237,8 @@ def _bias_rows(bias, E, N, dtype, dev):
 def gather_gemm(X, W, Ind, *, w_layout="cn", precision=None, path=None, bias=None):
     """Operator G: ``Y[b,e,k,:] = X[b, Ind[b,e,k], :] @ Wv[e] (+ bias[e])`` with ``Wv = W`` ('cn', W is [E,C,N]) or
     ``W^T`` per expert ('nc', W is [E,N,C]).  X [B,T,C] -> Y [B,E,K,N], dtype of X.  ``bias`` ([E,N] or [E,1,N]) is
-    added in the kernel's epilogue."""
+    added in the kernel's epilogue.  ``path="paired"`` (16-bit tensors, N a multiple of 32 up to 256) runs the kernel on
+    pairs of SMs (``EGS_PATH_PAIRED``); it raises for shapes that kernel does not take."""
     lib = _lib.load()
     if X.dim() != 3 or W.dim() != 3 or Ind.dim() != 3:
         raise ValueError("expected X[B,T,C], W[E,.,.], Ind[B,E,K]")

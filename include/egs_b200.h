@@ -37,7 +37,12 @@ enum { EGS_I16 = 0, EGS_I32 = 1, EGS_I64 = 2 };
 enum { EGS_PREC_STRICT = 0, EGS_PREC_TF32 = 1 };
 /* Kernel family.  AUTO picks the tcgen05 tensor-core kernels when the shape is eligible (row pitches
  * multiples of 16 bytes, 16-byte aligned bases) and the generic CUDA-core kernels otherwise. */
-enum { EGS_PATH_AUTO = 0, EGS_PATH_GENERIC = 1, EGS_PATH_TENSOR = 2 };
+enum { EGS_PATH_AUTO = 0, EGS_PATH_GENERIC = 1, EGS_PATH_TENSOR = 2,
+       /* egs_gather_gemm / egs_gather_gemm_bias only, 16-bit tensors, N a multiple of 32 and at most 256, C a multiple of 8,
+        * Y 32-byte aligned: the persistent kernel on pairs of SMs (thread-block clusters of two, tcgen05.mma.cta_group::2, each
+        * CTA staging half of every W tile).  Same results as EGS_PATH_TENSOR; never chosen by EGS_PATH_AUTO (it measured a few
+        * per cent slower); EGS_ERR_UNSUPPORTED for any other operator or shape. */
+       EGS_PATH_PAIRED = 3 };
 /* W memory layout relative to the contraction: CN = [E, C, N] (C rows of N), NC = [E, N, C]. */
 enum { EGS_W_CN = 0, EGS_W_NC = 1 };
 /* Output layout of the weight-gradient operator. */
