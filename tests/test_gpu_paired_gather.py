@@ -81,3 +81,20 @@ def test_paired_path_refuses_what_it_does_not_take():
         ops.gemm_scatter(torch.randn(2, 2, 4, 64, device=dev).bfloat16(), W.bfloat16(), Ind, 32, path="paired")
     with pytest.raises(ValueError):
         ops.set_path("paired")
+
+
+def test_paired_gather_at_the_benchmark_shard_size():
+    """cfg4 at the per-GPU shard (B=64): 512 tiles over 74 CTA pairs, i.e. the persistent walk, the accumulator hand-over
+    between tiles and the expert-fastest tile order are all exercised; element by element against the single-CTA kernel."""
+    from expertscattergather_b200 import ops, workloads as wl
+    dev = torch.device("cuda", 0)
+    w = wl.WORKLOADS["cfg4"]
+    d = {k: v.to(dev) for k, v in wl.make_inputs(w, B=64).items()}
+    for X, W, layout in ((d["X"], d["Wg"], "cn"), (d["G"], d["Ws"], "nc")):
+        Yp = ops.gather_gemm(X, W, d["Ind"], w_layout=layout, path="paired")
+        Yt = ops.gather_gemm(X, W, d["Ind"], w_layout=layout, path="tensor")
+        ops.check_status()
+        scale = Yt.float().abs().max().item()
+        assert (Yp.float() - Yt.float()).abs().max().item() <= 8e-3 * scale, layout
+        # same products, float32 accumulation in both: most elements agree to the last bit
+        assert (Yp == Yt).float().mean().item() > 0.9, layout
